@@ -1,7 +1,7 @@
 # Convenience targets (everything is plain python underneath).
 PY ?= python
 
-.PHONY: build test test-gpu bench smoke sass-check reference clean
+.PHONY: build test test-gpu bench smoke reference clean
 
 build:            ## nvcc -gencode arch=compute_100a,code=sm_100a -> swiftllm_b200/libswiftllm_b200.so
 	$(PY) -m swiftllm_b200.build
@@ -17,9 +17,6 @@ bench: build      ## one JSON line: decode tokens/s of BASELINE.json configs[1] 
 
 smoke: build
 	$(PY) -c "import __graft_entry__ as g; g.smoke()"
-
-sass-check: build ## validated kernels still compile to their validated instruction streams
-	$(PY) -m pytest tests/test_cabi.py -q -k validated
 
 reference:        ## the unmodified reference under baseline/_ref (for scripts/ref_triton_bench.py / the reference_triton block of bench.py)
 	bash scripts/install_reference.sh
