@@ -275,11 +275,16 @@ int sllm_latent_attention(const void* q_lat, int64_t q_lat_stride_t, int64_t q_l
 /* ---- Gated sliding-window attention with grouped key/value heads over a paged cache of per-token rows
  * [k (num_kv_heads x dk, rotary applied) | v (num_kv_heads x dv)] (new).  cache: [num_blocks, n_slots, block_size,
  * num_kv_heads * (dk + dv)] (dtype); tok_seq / tok_pos, cosb / sinb and rot_dims as for latent attention.
- * window_kv_store: k [T, num_kv_heads * dk] and v [T, num_kv_heads * dv] (row strides in elements) -> the tokens' cache rows. */
+ * window_kv_store: k [T, num_kv_heads * dk] and v [T, num_kv_heads * dv] (row strides in elements) -> the tokens' cache rows.
+ * Options shared with window_attention: pair_halves = 1 pairs entry i with i + rot_dims / 2 (0: entries 2i and 2i + 1);
+ * qk_norm_eps >= 0 divides every rotated key / query head by sqrt(mean of its squares + eps) (< 0: off); vcos / vsin (fp32
+ * [T, dv / 2], or NULL) turn the value of every head by the token's position before it is stored, and window_attention turns
+ * each head's output back by the query's position. */
 int sllm_window_kv_store(const void* k, int64_t k_row_stride, const void* v, int64_t v_row_stride, const void* cosb,
                          const void* sinb, const void* tok_seq, const void* tok_pos, const void* block_table,
                          int max_blocks_per_seq, void* cache, int n_slots, int slot, int block_size, int64_t num_tokens,
-                         int num_kv_heads, int dk, int dv, int rot_dims, sllm_dtype_t dtype, sllm_stream_t stream);
+                         int num_kv_heads, int dk, int dv, int rot_dims, int pair_halves, float qk_norm_eps, const void* vcos,
+                         const void* vsin, sllm_dtype_t dtype, sllm_stream_t stream);
 /* window_attention: per token i at position p and query head h (key/value head h / (num_heads / num_kv_heads)), over the cached
  * positions max(0, p - window + 1) .. p (all of 0 .. p when window <= 0):
  *   out[i, h, :dv] = sigmoid(gate[i, h, :dv]) * sum_j p_j v_j,   p_j = exp(s_j) / (sink + sum_j' exp(s_j')),
@@ -289,14 +294,63 @@ int sllm_window_kv_store(const void* k, int64_t k_row_stride, const void* v, int
  * tokens are grouped into CTAs; any value in 0 .. num_tokens gives the same result).
  * 16-bit dtypes with dk, dv multiples of 16 and <= 128 run on tensor cores (mma.sync over tokens x heads of a key/value group);
  * other shapes and SLLM_F32 run the fp32 CUDA-core kernel.  sllm_window_attention_set_simt(1) forces the latter (returns the
- * old setting). */
+ * old setting).  softcap > 0: s_j <- softcap * tanh(s_j / softcap); out_scale multiplies the output. */
 int sllm_window_attention_set_simt(int on);
 int sllm_window_attention(const void* q, int64_t q_stride_t, const void* cosb, const void* sinb, const void* gate,
                           int64_t gate_stride_t, const void* cache, int n_slots, int slot, int block_size,
                           const void* block_table, int max_blocks_per_seq, const void* tok_seq, const void* tok_pos, void* out,
                           int64_t out_stride_t, int64_t num_tokens, int64_t num_prefill_tokens, int num_heads, int num_kv_heads,
-                          int dk, int dv, int rot_dims, int window, float scale, int sink, sllm_dtype_t dtype,
+                          int dk, int dv, int rot_dims, int window, float scale, int sink, int pair_halves, float qk_norm_eps,
+                          float softcap, const void* vcos, const void* vsin, float out_scale, sllm_dtype_t dtype,
                           sllm_stream_t stream);
+
+/* ---- Sequential blocks on an fp32 residual stream whose sublayer OUTPUTS are normalised (new, stream_ops.cu).
+ * embed_pair_hash: x[t] (fp32) = embed[tokens[t]] + pairs[row], row = (previous * mul_prev + token * mul_cur) mod buckets with
+ * `previous` the token one position earlier (the row above, or last_token[tok_seq[t]] (int32 per sequence row) when the step
+ * starts there); a token at position 0 takes row `buckets`.  pairs may be NULL (no pair table).  x_copy (fp32, may be NULL)
+ * gets the same values; h gets their rounding to dtype.  store_last_tokens then records every segment's last token. */
+int sllm_embed_pair_hash(const void* tokens, const void* tok_seq, const void* tok_pos, const void* last_token, const void* embed,
+                         const void* pairs, int buckets, int64_t mul_prev, int64_t mul_cur, void* x, void* x_copy, void* h,
+                         int64_t num_tokens, int width, sllm_dtype_t dtype, sllm_stream_t stream);
+int sllm_store_last_tokens(const void* tokens, const void* seg_starts, const void* seq_ids, void* last_token, int num_segs,
+                           sllm_stream_t stream);
+/* postnorm_add_mix: X = x + gain[0] * y / sqrt(mean(y^2) + eps) per row (X = x when y is NULL); history (fp32
+ * [slots, T, width], may be NULL) slot `slot` <- X; with mix (fp32 [slot + 1], may be NULL) x <- sum_j mix[j] * history[j], else
+ * x <- X; h <- x rounded to dtype.  x fp32 [T, width] in place, y dtype, gain fp32 on the device. */
+int sllm_postnorm_add_mix(void* x, const void* y, const void* gain, float eps, void* history, int slot, const void* mix, void* h,
+                          int64_t num_tokens, int width, sllm_dtype_t dtype, sllm_stream_t stream);
+int sllm_tanh_cap_inplace(void* x, int64_t n, float cap, sllm_dtype_t dtype, sllm_stream_t stream);
+/* moe_route_sigmoid: logits fp32 [T, experts] -> weights fp32 [T, experts]: s = sigmoid(logits); the `top` experts with the
+ * largest s + bias (fp32 [experts] or NULL) get weight s, the others 0.  moe_silu_glu_scale: u [T, experts * 2 * ff] (per expert
+ * [gate | up]) -> y [T, experts * ff] = silu(gate) * up * weights[t, expert]. */
+int sllm_moe_route_sigmoid(const void* logits, const void* bias, void* weights, int64_t num_tokens, int experts, int top,
+                           sllm_stream_t stream);
+int sllm_moe_silu_glu_scale(const void* u, const void* weights, void* y, int64_t num_tokens, int experts, int ff,
+                            sllm_dtype_t dtype, sllm_stream_t stream);
+
+/* ---- Recurrent mixers with per-sequence state (new, recurrent.cu).  A step's rows seg_starts[b] .. seg_starts[b + 1] - 1 are
+ * consecutive positions of sequence row seq_ids[b]; a segment at position 0 starts from the zero state.
+ * causal_conv: u[t, c] = bias[c] + sum_k w[c, taps - 1 - k] * xin[t - k, c] over the sequence (tail: dtype [rows, taps - 1,
+ * channels], the sequence's last inputs before this step; xin row stride in elements).
+ * rglru_scan: gates dtype [blocks, T, 2 * channels / blocks] (logits of the recurrence gate, then of the input gate, per block);
+ * a = exp(rate[c] * sigmoid(r)); S <- a S + sqrt(1 - a^2) sigmoid(i) u; out = S * gelu_tanh(ybr); state fp32 [rows, channels];
+ * also moves `tail` on by the segment's inputs xin. */
+int sllm_causal_conv(const void* xin, int64_t xin_stride, const void* w, const void* bias, const void* tail, const void* tok_seq,
+                     const void* tok_pos, void* u, int64_t num_tokens, int channels, int taps, sllm_dtype_t dtype,
+                     sllm_stream_t stream);
+int sllm_rglru_scan(const void* u, const void* gates, int blocks, const void* ybr, int64_t y_stride, const void* rate,
+                    const void* xin, int64_t xin_stride, void* state, void* tail, const void* seg_starts, const void* seq_ids,
+                    const void* tok_pos, void* out, int64_t num_tokens, int num_segs, int channels, int taps, sllm_dtype_t dtype,
+                    sllm_stream_t stream);
+/* linear_attention: per head S <- decay[h] S + silu(k) silu(v)^T, out[t, h] (fp32 [T, heads * dv]) = S^T silu(q); q, k
+ * [T, heads * dk], v [T, heads * dv] pre-activation (row strides in elements); state fp32 [rows, heads, dk, dv].
+ * gated_rmsnorm: out = x / sqrt(mean(x^2) + eps) * weight * sigmoid(gate) * out_scale; x fp32 [T, n], weight fp32 [n], gate
+ * dtype logits (may be NULL), out dtype (row strides in elements). */
+int sllm_linear_attention(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v, int64_t v_stride,
+                          const void* decay, void* state, const void* seg_starts, const void* seq_ids, const void* tok_pos,
+                          void* out, int num_segs, int num_heads, int dk, int dv, sllm_dtype_t dtype, sllm_stream_t stream);
+int sllm_gated_rmsnorm(const void* x, const void* weight, const void* gate, int64_t gate_stride, float eps, float out_scale,
+                       void* out, int64_t out_stride, int64_t num_tokens, int n, sllm_dtype_t dtype, sllm_stream_t stream);
 
 #ifdef __cplusplus
 }

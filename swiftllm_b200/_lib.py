@@ -55,10 +55,20 @@ SIGNATURES = {
     "sllm_latent_attention_set_simt": (_I, [_I]),
     "sllm_latent_attention": (_I, [_P, _L, _L, _P, _L, _L, _P, _P, _P, _L, _P, _I, _I, _I, _P, _I, _P, _P, _P, _L, _L, _L, _I, _I,
                                    _I, _I, _I, _F, _I, _P, _I, _P]),
-    "sllm_window_kv_store": (_I, [_P, _L, _P, _L, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _L, _I, _I, _I, _I, _I, _P]),
+    "sllm_window_kv_store": (_I, [_P, _L, _P, _L, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _L, _I, _I, _I, _I, _I, _F, _P, _P, _I, _P]),
     "sllm_window_attention_set_simt": (_I, [_I]),
     "sllm_window_attention": (_I, [_P, _L, _P, _P, _P, _L, _P, _I, _I, _I, _P, _I, _P, _P, _P, _L, _L, _L, _I, _I, _I, _I, _I, _I,
-                                   _F, _I, _I, _P]),
+                                   _F, _I, _I, _F, _F, _P, _P, _F, _I, _P]),
+    "sllm_embed_pair_hash": (_I, [_P, _P, _P, _P, _P, _P, _I, _L, _L, _P, _P, _P, _L, _I, _I, _P]),
+    "sllm_store_last_tokens": (_I, [_P, _P, _P, _P, _I, _P]),
+    "sllm_postnorm_add_mix": (_I, [_P, _P, _P, _F, _P, _I, _P, _P, _L, _I, _I, _P]),
+    "sllm_tanh_cap_inplace": (_I, [_P, _L, _F, _I, _P]),
+    "sllm_moe_route_sigmoid": (_I, [_P, _P, _P, _L, _I, _I, _P]),
+    "sllm_moe_silu_glu_scale": (_I, [_P, _P, _P, _L, _I, _I, _I, _P]),
+    "sllm_causal_conv": (_I, [_P, _L, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _P]),
+    "sllm_rglru_scan": (_I, [_P, _P, _I, _P, _L, _P, _P, _L, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _P]),
+    "sllm_linear_attention": (_I, [_P, _L, _P, _L, _P, _L, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "sllm_gated_rmsnorm": (_I, [_P, _P, _P, _L, _F, _F, _P, _L, _L, _I, _I, _P]),
 }
 
 _lib = None

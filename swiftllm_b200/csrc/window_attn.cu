@@ -6,21 +6,45 @@
 // Every token of the step is a query with its own (block-table row, position): prompt portions and single decoded tokens go
 // through the same kernel, so the result at a position does not depend on how its sequence was cut into steps.  A query at
 // position p sees the positions max(0, p - window + 1) .. p (window <= 0: all of 0 .. p).  Rotary pairs are interleaved
-// ((2i, 2i+1), the first rot_dims entries of a head; the rest pass through).  Softmax, rotation and the weighted sum of values
+// ((2i, 2i+1)) or halves ((i, i + rot_dims/2)) of the first rot_dims entries of a head; the rest pass through; the caller's
+// cos / sin tables carry the frequencies (and any common factor on both).  Softmax, rotation and the weighted sum of values
 // run in fp32 for every storage type.
+// Options that other designs use (all off for the plain gated window attention):
+//   qk_norm_eps >= 0   rotated queries and keys are divided by sqrt(mean over the head + eps)
+//   softcap > 0        score <- softcap * tanh(score / softcap) after the scale
+//   vcos / vsin        the value at position j is stored turned by j (pairs (m, m + dv/2) when `halves`, else (2m, 2m+1), angle
+//                      tables [T, dv/2]) and the head's output at position i is turned back by -i
+//   out_scale          factor on the output (a mixer that is summed with another one folds its weight here)
 #include "mma_helpers.cuh"
 #include "typed_io.cuh"
 
 namespace sllm {
 
+// entry j of a head row x turned by the token's angles (cs / sn: the token's table rows); entries from rot_dims on pass through
+template <typename T>
+__device__ __forceinline__ float rot_entry(const T* __restrict__ x, int j, int rot_dims, int halves, const float* __restrict__ cs,
+                                           const float* __restrict__ sn) {
+    if (j >= rot_dims) return ldf(x + j);
+    if (halves) {
+        const int half = rot_dims >> 1;
+        if (j < half) return ldf(x + j) * cs[j] - ldf(x + j + half) * sn[j];
+        return ldf(x + j) * cs[j - half] + ldf(x + j - half) * sn[j - half];
+    }
+    const int i = j >> 1;
+    const float a = ldf(x + 2 * i), b = ldf(x + 2 * i + 1);
+    return (j & 1) ? b * cs[i] + a * sn[i] : a * cs[i] - b * sn[i];
+}
+
 // ------------------------------------------------------------------ cache store
-// One CTA per token: rotate k, copy v, write the token's row of cache slot `slot`.
+// One CTA per token, one warp per key/value head at a time: rotate k (and divide it by its root mean square), rotate or copy v,
+// write the token's row of cache slot `slot`.
 template <typename T>
 __global__ void __launch_bounds__(128) window_kv_store_kernel(
     const T* __restrict__ k, int64_t k_stride, const T* __restrict__ v, int64_t v_stride, const float* __restrict__ cosb,
     const float* __restrict__ sinb, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
     const int* __restrict__ block_table, int max_blocks_per_seq, T* __restrict__ cache, int n_slots, int slot, int block_size,
-    int G, int dk, int dv, int rot_dims) {
+    int G, int dk, int dv, int rot_dims, int halves, float qk_norm_eps, const float* __restrict__ vcos,
+    const float* __restrict__ vsin) {
     const int64_t t = blockIdx.x;
     const int pos = tok_pos[t];
     const int blk = block_table[(int64_t)tok_seq[t] * max_blocks_per_seq + pos / block_size];
@@ -28,21 +52,27 @@ __global__ void __launch_bounds__(128) window_kv_store_kernel(
     T* dst = cache + (((int64_t)blk * n_slots + slot) * block_size + pos % block_size) * (kw + vw);
     const T* kr = k + t * k_stride;
     const T* vr = v + t * v_stride;
-    const int half = rot_dims >> 1;
-    for (int c = threadIdx.x; c < kw; c += blockDim.x) {
-        const int j = c % dk, base = c - j;
-        float o;
-        if (j < rot_dims) {
-            const int i = j >> 1;
-            const float a = ldf(kr + base + 2 * i), b = ldf(kr + base + 2 * i + 1);
-            const float cs = cosb[t * half + i], sn = sinb[t * half + i];
-            o = (j & 1) ? b * cs + a * sn : a * cs - b * sn;
-        } else {
-            o = ldf(kr + c);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const float* cs = cosb != nullptr ? cosb + t * (rot_dims >> 1) : nullptr;
+    const float* sn = sinb != nullptr ? sinb + t * (rot_dims >> 1) : nullptr;
+    for (int g = warp; g < G; g += nwarps) {
+        const T* x = kr + g * dk;
+        float inv = 1.f;
+        if (qk_norm_eps >= 0.f) {
+            float ss = 0.f;
+            for (int j = lane; j < dk; j += 32) { const float o = rot_entry(x, j, rot_dims, halves, cs, sn); ss += o * o; }
+            inv = 1.f / sqrtf(warp_sum(ss) / (float)dk + qk_norm_eps);
         }
-        stf(dst + c, o);
+        for (int j = lane; j < dk; j += 32) stf(dst + g * dk + j, rot_entry(x, j, rot_dims, halves, cs, sn) * inv);
+        const T* y = vr + g * dv;
+        if (vcos != nullptr) {
+            const float* vc = vcos + t * (dv >> 1);
+            const float* vs = vsin + t * (dv >> 1);
+            for (int j = lane; j < dv; j += 32) stf(dst + kw + g * dv + j, rot_entry(y, j, dv, halves, vc, vs));
+        } else {
+            for (int j = lane; j < dv; j += 32) dst[kw + g * dv + j] = y[j];
+        }
     }
-    for (int c = threadIdx.x; c < vw; c += blockDim.x) dst[kw + c] = vr[c];
 }
 
 // ------------------------------------------------------------------ attention (fp32 CUDA cores)
@@ -58,13 +88,15 @@ __global__ void __launch_bounds__(WA_MAX_HPB * 32) window_attn_kernel(
     const T* __restrict__ cache, int n_slots, int slot, int block_size,
     const int* __restrict__ block_table, int max_blocks_per_seq, const int* __restrict__ tok_seq,
     const int* __restrict__ tok_pos, T* __restrict__ out, int64_t out_stride_t,  // [T, H, dv]
-    int H, int G, int dk, int dv, int rot_dims, int window, float scale, float sink) {
+    int H, int G, int dk, int dv, int rot_dims, int window, float scale, float sink, int halves, float qk_norm_eps,
+    float softcap, const float* __restrict__ vcos, const float* __restrict__ vsin, float out_scale) {
     extern __shared__ float smem[];
     const int KP = dk + 1;
     const int hpb = blockDim.x >> 5;
     float* qs = smem;                          // [hpb][dk]
     float* kt = qs + hpb * dk;                 // [WA_TILE][dk + 1]
     float* vt = kt + WA_TILE * KP;             // [WA_TILE][dv]
+    float* os = vt + WA_TILE * dv;             // [hpb][dv]: the head's output before it is turned back (vcos only)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t t = blockIdx.x;
     const int h = blockIdx.y * hpb + warp;
@@ -76,19 +108,16 @@ __global__ void __launch_bounds__(WA_MAX_HPB * 32) window_attn_kernel(
     {
         float* qw = qs + warp * dk;
         const T* qr = q + t * q_stride_t + (int64_t)h * dk;
-        const int half = rot_dims >> 1;
+        const float* cs = cosb != nullptr ? cosb + t * (rot_dims >> 1) : nullptr;
+        const float* sn = sinb != nullptr ? sinb + t * (rot_dims >> 1) : nullptr;
+        float ss = 0.f;
         for (int j = lane; j < dk; j += 32) {
-            float o;
-            if (j < rot_dims) {
-                const int i = j >> 1;
-                const float a = ldf(qr + 2 * i), b = ldf(qr + 2 * i + 1);
-                const float cs = cosb[t * half + i], sn = sinb[t * half + i];
-                o = (j & 1) ? b * cs + a * sn : a * cs - b * sn;
-            } else {
-                o = ldf(qr + j);
-            }
-            qw[j] = o * scale;
+            const float o = rot_entry(qr, j, rot_dims, halves, cs, sn);
+            qw[j] = o;
+            ss += o * o;
         }
+        const float f = qk_norm_eps >= 0.f ? scale / sqrtf(warp_sum(ss) / (float)dk + qk_norm_eps) : scale;
+        for (int j = lane; j < dk; j += 32) qw[j] *= f;            // every lane rescales what it wrote itself
     }
 
     // a sink takes part in the normalisation only: it enters the running (maximum, sum) as a key of score 0 without a value
@@ -116,7 +145,7 @@ __global__ void __launch_bounds__(WA_MAX_HPB * 32) window_attn_kernel(
             const float* kr = kt + lane * KP;
             float a = 0.f;
             for (int d = 0; d < dk; d++) a += qw[d] * kr[d];
-            s = a;
+            s = softcap > 0.f ? softcap * tanhf(a / softcap) : a;
         }
         const float m_new = fmaxf(m, warp_max(s));          // finite: key `base` is always visible
         const float alpha = expf(m - m_new);                // 0 on the first tile without a sink (m = -inf)
@@ -135,14 +164,38 @@ __global__ void __launch_bounds__(WA_MAX_HPB * 32) window_attn_kernel(
         }
         m = m_new;
     }
-    const float denom = l;
+    float denom = l;
     T* o = out + t * out_stride_t + (int64_t)h * dv;
     const T* gr = gate != nullptr ? gate + t * gate_stride_t + (int64_t)h * dv : nullptr;
+    if (vcos != nullptr) {
+        // the sum of turned values is turned back by the query's own position: pair (a, b) -> (a c + b s, b c - a s)
+        float* ow = os + warp * dv;
+#pragma unroll
+        for (int k = 0; k < KR; k++) {
+            const int d = lane + 32 * k;
+            if (d < dv) ow[d] = acc[k] / denom;
+        }
+        __syncwarp();
+        const int hv = dv >> 1;
+        const float* vc = vcos + t * hv;
+        const float* vs = vsin + t * hv;
+#pragma unroll
+        for (int k = 0; k < KR; k++) {
+            const int d = lane + 32 * k;
+            if (d < dv) {
+                int m, second;
+                if (halves) { second = d >= hv; m = second ? d - hv : d; } else { second = d & 1; m = d >> 1; }
+                const float a = halves ? ow[m] : ow[2 * m], b = halves ? ow[m + hv] : ow[2 * m + 1];
+                acc[k] = second ? b * vc[m] - a * vs[m] : a * vc[m] + b * vs[m];
+            }
+        }
+        denom = 1.f;
+    }
 #pragma unroll
     for (int k = 0; k < KR; k++) {
         const int d = lane + 32 * k;
         if (d < dv) {
-            float y = acc[k] / denom;
+            float y = acc[k] / denom * out_scale;
             if (gr != nullptr) y *= 1.f / (1.f + expf(-ldf(gr + d)));
             stf(o + d, y);
         }
@@ -169,7 +222,8 @@ __global__ void __launch_bounds__(128, WT_KEYS == 32 ? 3 : 2) window_attn_mma_ke
     const T* __restrict__ gate, int64_t gate_stride_t, const T* __restrict__ cache, int n_slots, int slot, int block_size,
     const int* __restrict__ block_table, int max_blocks_per_seq, const int* __restrict__ tok_seq,
     const int* __restrict__ tok_pos, T* __restrict__ out, int64_t out_stride_t, int row0, int nrows, int qt, int hq, int hqp_log2,
-    int H, int G, int dk, int dv, int rot_dims, int window, float scale_log2, float sink) {
+    int H, int G, int dk, int dv, int rot_dims, int window, float scale_log2, float sink, int halves, float qk_norm_eps,
+    float softcap, const float* __restrict__ vcos, const float* __restrict__ vsin, float out_scale) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int PQ = dk * 2 + 16, PK = dk * 2 + 16, PV = dv * 2 + 16;            // row pitches in bytes
     unsigned char* Qs = smem_raw;                                              // [64][PQ]
@@ -183,6 +237,9 @@ __global__ void __launch_bounds__(128, WT_KEYS == 32 ? 3 : 2) window_attn_mma_ke
     const int row_elems = G * (dk + dv);
     const int ck = dk >> 3, cv = dv >> 3;                                      // 16-byte chunks per key / value row
     const int half = rot_dims >> 1;
+    // with a score cap: cap * tanh(s * scale / cap), then to base 2
+    const float cap_in = softcap > 0.f ? scale_log2 * 0.6931471805599453f / softcap : 0.f;
+    const float cap_out = softcap * 1.4426950408889634f;
 
     for (int i0 = 0; i0 < ntok;) {
         // ---- the segment: tokens t_first + i0 .. + n - 1 of one sequence at consecutive positions
@@ -218,21 +275,32 @@ __global__ void __launch_bounds__(128, WT_KEYS == 32 ? 3 : 2) window_attn_mma_ke
         };
         load_tile(0);
 
-        // ---- queries of the segment: rotated in fp32, rounded to the storage type; dead rows are zeros
-        for (int r = tid >> 1; r < WT_ROWS; r += 64) {                         // two threads per row
+        // ---- queries of the segment: rotated (and divided by their root mean square) in fp32, rounded to the storage type;
+        // dead rows are zeros.  Two threads per row (neighbouring lanes), each takes every other pair of entries.
+        {
+            const int r = tid >> 1;                                            // 128 threads, 64 rows: one row per thread pair
             const int j = r >> hqp_log2, hh = r & (hqp - 1);
             const bool live = j < n && hh < hq;
             const int64_t t = ts + j;
             const T* qr = q + t * q_stride_t + (int64_t)(g * hq + hh) * dk;
+            const float* cs = cosb != nullptr ? cosb + t * half : nullptr;
+            const float* sn = sinb != nullptr ? sinb + t * half : nullptr;
+            float inv = 1.f;
+            if (qk_norm_eps >= 0.f) {
+                float ss = 0.f;
+                if (live)
+                    for (int i = tid & 1; i < (dk >> 1); i += 2) {
+                        const float a = rot_entry(qr, 2 * i, rot_dims, halves, cs, sn), b = rot_entry(qr, 2 * i + 1, rot_dims, halves, cs, sn);
+                        ss += a * a + b * b;
+                    }
+                ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+                inv = 1.f / sqrtf(ss / (float)dk + qk_norm_eps);
+            }
             for (int i = tid & 1; i < (dk >> 1); i += 2) {
                 float a = 0.f, b = 0.f;
                 if (live) {
-                    a = ldf(qr + 2 * i); b = ldf(qr + 2 * i + 1);
-                    if (2 * i < rot_dims) {
-                        const float cs = cosb[t * half + i], sn = sinb[t * half + i];
-                        const float ra = a * cs - b * sn, rb = b * cs + a * sn;
-                        a = ra; b = rb;
-                    }
+                    a = rot_entry(qr, 2 * i, rot_dims, halves, cs, sn) * inv;
+                    b = rot_entry(qr, 2 * i + 1, rot_dims, halves, cs, sn) * inv;
                 }
                 *reinterpret_cast<uint32_t*>(Qs + r * PQ + i * 4) = pack2<T>(a, b);
             }
@@ -288,8 +356,10 @@ __global__ void __launch_bounds__(128, WT_KEYS == 32 ? 3 : 2) window_attn_mma_ke
                     for (int e = 0; e < 2; e++) {
                         const int kp = base + nt * 8 + (lane & 3) * 2 + e;
                         const bool va = live_a && kp <= pos_a && kp >= lo_a, vb = live_b && kp <= pos_b && kp >= lo_b;
-                        sc[nt][e] = va ? sc[nt][e] * scale_log2 : -INFINITY;
-                        sc[nt][2 + e] = vb ? sc[nt][2 + e] * scale_log2 : -INFINITY;
+                        const float sa = softcap > 0.f ? cap_out * tanhf(sc[nt][e] * cap_in) : sc[nt][e] * scale_log2;
+                        const float sb = softcap > 0.f ? cap_out * tanhf(sc[nt][2 + e] * cap_in) : sc[nt][2 + e] * scale_log2;
+                        sc[nt][e] = va ? sa : -INFINITY;
+                        sc[nt][2 + e] = vb ? sb : -INFINITY;
                         mx_a = fmaxf(mx_a, sc[nt][e]);
                         mx_b = fmaxf(mx_b, sc[nt][2 + e]);
                     }
@@ -329,9 +399,46 @@ __global__ void __launch_bounds__(128, WT_KEYS == 32 ? 3 : 2) window_attn_mma_ke
             __syncthreads();                                                   // stage it & 1 may be overwritten by tile it + 2
         }
 
-        // ---- normalise, gate, store
+        // ---- normalise, (turn back,) gate, store
         l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
         l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+        if (vcos != nullptr) {
+            // values were stored turned by their own position: the normalised sums go through shared memory (the tiles are done
+            // with: the loop ended on a barrier), where every pair is turned back by the query's position
+            float* Os = reinterpret_cast<float*>(smem_raw);                    // [64][dv]
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int r = e ? r_b : r_a;
+                const float inv = 1.f / (e ? l_b : l_a);
+#pragma unroll
+                for (int nt = 0; nt < DMAX / 8; nt++) {
+                    const int d = nt * 8 + (lane & 3) * 2;
+                    if (d < dv) { Os[r * dv + d] = o[nt][2 * e] * inv; Os[r * dv + d + 1] = o[nt][2 * e + 1] * inv; }
+                }
+            }
+            __syncthreads();
+            const int hv = dv >> 1;
+            for (int idx = tid; idx < WT_ROWS * hv; idx += 128) {
+                const int r = idx / hv, m = idx - r * hv;
+                const int j = r >> hqp_log2, hh = r & (hqp - 1);
+                if (j >= n || hh >= hq) continue;
+                const int64_t t = ts + j;
+                const int da = halves ? m : 2 * m, db = halves ? m + hv : 2 * m + 1;
+                const float a = Os[r * dv + da], b = Os[r * dv + db];
+                const float c = vcos[t * hv + m], sn = vsin[t * hv + m];
+                float ya = (a * c + b * sn) * out_scale, yb = (b * c - a * sn) * out_scale;
+                T* orow = out + t * out_stride_t + (int64_t)(g * hq + hh) * dv;
+                if (gate != nullptr) {
+                    const T* grow = gate + t * gate_stride_t + (int64_t)(g * hq + hh) * dv;
+                    ya *= 1.f / (1.f + __expf(-ldf(grow + da)));
+                    yb *= 1.f / (1.f + __expf(-ldf(grow + db)));
+                }
+                stf(orow + da, ya);
+                stf(orow + db, yb);
+            }
+            i0 += n;
+            continue;                                                          // the next segment starts with a barrier
+        }
 #pragma unroll
         for (int e = 0; e < 2; e++) {
             const bool live = e ? live_b : live_a;
@@ -339,7 +446,7 @@ __global__ void __launch_bounds__(128, WT_KEYS == 32 ? 3 : 2) window_attn_mma_ke
             const int r = e ? r_b : r_a;
             const int64_t t = ts + (r >> hqp_log2);
             const int h = g * hq + (r & (hqp - 1));
-            const float inv = 1.f / (e ? l_b : l_a);
+            const float inv = out_scale / (e ? l_b : l_a);
             T* orow = out + t * out_stride_t + (int64_t)h * dv;
             const T* grow = gate != nullptr ? gate + t * gate_stride_t + (int64_t)h * dv : nullptr;
 #pragma unroll
@@ -367,7 +474,8 @@ static int launch_window_attn_mma(const void* q, int64_t q_stride_t, const void*
                                   int64_t gate_stride_t, const void* cache, int n_slots, int slot, int block_size,
                                   const void* block_table, int max_blocks_per_seq, const void* tok_seq, const void* tok_pos,
                                   void* out, int64_t out_stride_t, int64_t num_tokens, int64_t num_prefill, int H, int G, int dk,
-                                  int dv, int rot_dims, int window, float scale, float sink, cudaStream_t stream) {
+                                  int dv, int rot_dims, int window, float scale, float sink, int halves, float qk_norm_eps,
+                                  float softcap, const void* vcos, const void* vsin, float out_scale, cudaStream_t stream) {
     static unsigned long long attr_mask = 0;
     const int hq = H / G;
     int hqp_log2 = 0;
@@ -389,11 +497,13 @@ static int launch_window_attn_mma(const void* q, int64_t q_stride_t, const void*
         // measured on B200 (128 + 128 per head): prompt portions 24 - 26 % faster with 32-key tiles (three CTAs per SM instead of
         // two); decoded tokens faster with 64-key tiles at 512 CTAs (357 vs 385 us), with 32-key tiles at 2048 CTAs (950 vs 1220 us)
         const int keys = (k == 0 || count * G >= 7 * (int64_t)num_sms) ? 32 : 64;
-        const size_t smem = (size_t)WT_ROWS * (dk * 2 + 16) + 2 * (size_t)keys * ((dk * 2 + 16) + (dv * 2 + 16));
+        size_t smem = (size_t)WT_ROWS * (dk * 2 + 16) + 2 * (size_t)keys * ((dk * 2 + 16) + (dv * 2 + 16));
+        if (vcos != nullptr && smem < (size_t)WT_ROWS * dv * sizeof(float)) smem = (size_t)WT_ROWS * dv * sizeof(float);
         (keys == 32 ? kern_prompt : kern_decode)<<<dim3((unsigned)cdiv(count, qt), (unsigned)G), 128, smem, stream>>>(
             (const T*)q, q_stride_t, (const float*)cosb, (const float*)sinb, (const T*)gate, gate_stride_t, (const T*)cache,
             n_slots, slot, block_size, (const int*)block_table, max_blocks_per_seq, (const int*)tok_seq, (const int*)tok_pos,
-            (T*)out, out_stride_t, (int)first, (int)count, qt, hq, hqp_log2, H, G, dk, dv, rot_dims, window, scale_log2, sink);
+            (T*)out, out_stride_t, (int)first, (int)count, qt, hq, hqp_log2, H, G, dk, dv, rot_dims, window, scale_log2, sink,
+            halves, qk_norm_eps, softcap, (const float*)vcos, (const float*)vsin, out_scale);
     }
     return check_launch("window_attention (tensor cores)");
 }
@@ -409,10 +519,11 @@ static int launch_window_attn(const void* q, int64_t q_stride_t, const void* cos
                               int64_t gate_stride_t, const void* cache, int n_slots, int slot, int block_size,
                               const void* block_table, int max_blocks_per_seq, const void* tok_seq, const void* tok_pos, void* out,
                               int64_t out_stride_t, int64_t num_tokens, int H, int G, int dk, int dv, int rot_dims, int window,
-                              float scale, float sink, cudaStream_t stream) {
+                              float scale, float sink, int halves, float qk_norm_eps, float softcap, const void* vcos,
+                              const void* vsin, float out_scale, cudaStream_t stream) {
     static unsigned long long attr_mask = 0;
     const int hpb = heads_per_cta(H / G);
-    const size_t smem = ((size_t)hpb * dk + (size_t)WA_TILE * (dk + 1) + (size_t)WA_TILE * dv) * sizeof(float);
+    const size_t smem = ((size_t)hpb * dk + (size_t)WA_TILE * (dk + 1) + (size_t)WA_TILE * dv + (size_t)hpb * dv) * sizeof(float);
     SLLM_REQUIRE(smem <= 200 * 1024, "window_attention: head sizes %d / %d need %zu bytes of shared memory", dk, dv, smem);
     auto kern = window_attn_kernel<T, KR>;
     if (first_use_on_this_device(attr_mask))
@@ -420,7 +531,8 @@ static int launch_window_attn(const void* q, int64_t q_stride_t, const void* cos
     kern<<<dim3((unsigned)num_tokens, (unsigned)(H / hpb)), hpb * 32, smem, stream>>>(
         (const T*)q, q_stride_t, (const float*)cosb, (const float*)sinb, (const T*)gate, gate_stride_t, (const T*)cache, n_slots,
         slot, block_size, (const int*)block_table, max_blocks_per_seq, (const int*)tok_seq, (const int*)tok_pos, (T*)out,
-        out_stride_t, H, G, dk, dv, rot_dims, window, scale, sink);
+        out_stride_t, H, G, dk, dv, rot_dims, window, scale, sink, halves, qk_norm_eps, softcap, (const float*)vcos,
+        (const float*)vsin, out_scale);
     return check_launch("window_attention");
 }
 
@@ -433,9 +545,12 @@ extern "C" {
 int sllm_window_kv_store(const void* k, int64_t k_row_stride, const void* v, int64_t v_row_stride, const void* cosb,
                          const void* sinb, const void* tok_seq, const void* tok_pos, const void* block_table,
                          int max_blocks_per_seq, void* cache, int n_slots, int slot, int block_size, int64_t num_tokens,
-                         int num_kv_heads, int dk, int dv, int rot_dims, sllm_dtype_t dtype, sllm_stream_t stream) {
+                         int num_kv_heads, int dk, int dv, int rot_dims, int pair_halves, float qk_norm_eps, const void* vcos,
+                         const void* vsin, sllm_dtype_t dtype, sllm_stream_t stream) {
     SLLM_REQUIRE(num_tokens >= 0 && num_kv_heads > 0 && dk > 0 && dv > 0 && rot_dims >= 0 && rot_dims <= dk && rot_dims % 2 == 0,
                  "window_kv_store: bad shape (kv heads %d, dk %d, dv %d, rot_dims %d)", num_kv_heads, dk, dv, rot_dims);
+    SLLM_REQUIRE((vcos == nullptr) == (vsin == nullptr) && (vcos == nullptr || dv % 2 == 0),
+                 "window_kv_store: turned values need both angle tables and an even value size (dv %d)", dv);
     SLLM_REQUIRE(slot >= 0 && slot < n_slots && block_size > 0, "window_kv_store: bad cache slot %d of %d", slot, n_slots);
     if (num_tokens == 0) return 0;
     SLLM_REQUIRE(k && v && tok_seq && tok_pos && block_table && cache && (rot_dims == 0 || (cosb && sinb)),
@@ -443,7 +558,7 @@ int sllm_window_kv_store(const void* k, int64_t k_row_stride, const void* v, int
     SLLM_DISPATCH_DTYPE_F32(dtype, (window_kv_store_kernel<T><<<(unsigned)num_tokens, 128, 0, (cudaStream_t)stream>>>(
         (const T*)k, k_row_stride, (const T*)v, v_row_stride, (const float*)cosb, (const float*)sinb, (const int*)tok_seq,
         (const int*)tok_pos, (const int*)block_table, max_blocks_per_seq, (T*)cache, n_slots, slot, block_size, num_kv_heads,
-        dk, dv, rot_dims)));
+        dk, dv, rot_dims, pair_halves, qk_norm_eps, (const float*)vcos, (const float*)vsin)));
     return check_launch("window_kv_store");
 }
 
@@ -457,8 +572,11 @@ int sllm_window_attention(const void* q, int64_t q_stride_t, const void* cosb, c
                           int64_t gate_stride_t, const void* cache, int n_slots, int slot, int block_size,
                           const void* block_table, int max_blocks_per_seq, const void* tok_seq, const void* tok_pos, void* out,
                           int64_t out_stride_t, int64_t num_tokens, int64_t num_prefill_tokens, int num_heads, int num_kv_heads,
-                          int dk, int dv, int rot_dims, int window, float scale, int sink, sllm_dtype_t dtype,
+                          int dk, int dv, int rot_dims, int window, float scale, int sink, int pair_halves, float qk_norm_eps,
+                          float softcap, const void* vcos, const void* vsin, float out_scale, sllm_dtype_t dtype,
                           sllm_stream_t stream) {
+    SLLM_REQUIRE((vcos == nullptr) == (vsin == nullptr) && (vcos == nullptr || dv % 2 == 0) && softcap >= 0.f,
+                 "window_attention: turned values need both angle tables and an even value size (dv %d); softcap >= 0", dv);
     SLLM_REQUIRE(num_tokens >= 0 && num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0 && dk > 0 && dv > 0 &&
                  dv <= 256 && rot_dims >= 0 && rot_dims <= dk && rot_dims % 2 == 0,
                  "window_attention: bad shape (heads %d / %d, dk %d, dv %d <= 256, rot_dims %d)", num_heads, num_kv_heads, dk,
@@ -475,7 +593,8 @@ int sllm_window_attention(const void* q, int64_t q_stride_t, const void* cosb, c
 #define WA_MMA(DMAX)                                                                                                        \
     SLLM_DISPATCH_DTYPE(dtype, return (launch_window_attn_mma<T, DMAX>(q, q_stride_t, cosb, sinb, gate, gate_stride_t, cache,  \
         n_slots, slot, block_size, block_table, max_blocks_per_seq, tok_seq, tok_pos, out, out_stride_t, num_tokens,         \
-        num_prefill_tokens, num_heads, num_kv_heads, dk, dv, rot_dims, window, scale, sinkw, (cudaStream_t)stream)))
+        num_prefill_tokens, num_heads, num_kv_heads, dk, dv, rot_dims, window, scale, sinkw, pair_halves, qk_norm_eps, softcap, \
+        vcos, vsin, out_scale, (cudaStream_t)stream)))
         if (dk <= 64 && dv <= 64) { WA_MMA(64); }
         else { WA_MMA(128); }
 #undef WA_MMA
@@ -483,7 +602,8 @@ int sllm_window_attention(const void* q, int64_t q_stride_t, const void* cosb, c
 #define WA_LAUNCH(KR)                                                                                                      \
     SLLM_DISPATCH_DTYPE_F32(dtype, return (launch_window_attn<T, KR>(q, q_stride_t, cosb, sinb, gate, gate_stride_t, cache,   \
         n_slots, slot, block_size, block_table, max_blocks_per_seq, tok_seq, tok_pos, out, out_stride_t, num_tokens,        \
-        num_heads, num_kv_heads, dk, dv, rot_dims, window, scale, sinkw, (cudaStream_t)stream)))
+        num_heads, num_kv_heads, dk, dv, rot_dims, window, scale, sinkw, pair_halves, qk_norm_eps, softcap, vcos, vsin,      \
+        out_scale, (cudaStream_t)stream)))
     if (dv <= 32) { WA_LAUNCH(1); }
     else if (dv <= 64) { WA_LAUNCH(2); }
     else if (dv <= 128) { WA_LAUNCH(4); }

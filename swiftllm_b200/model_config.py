@@ -100,10 +100,68 @@ class WindowAttentionSpec:
     scale: float
     sink: bool = True
     kv_from: Optional[int] = None   # every layer caches its own keys and values
+    gate: bool = True               # element-wise sigmoid gate on the output (projection `g`)
+    pair_halves: bool = False       # rotary pairs (i, i + rot_dims / 2) instead of (2i, 2i + 1)
+    # (factor, original context, fast turns, slow turns): pairs that make fewer than `slow` turns over the original context are
+    # slowed by `factor`, pairs that make more than `fast` are kept, a linear ramp between; cos and sin get 0.1 ln(factor) + 1
+    rot_scaling: Optional[tuple] = None
+    qk_unit_norm: bool = False      # rotated queries and keys are divided by their root mean square over the head
+    softcap: float = 0.0            # > 0: score <- softcap * tanh(score / softcap)
+    value_rotation: bool = False    # values are turned by their position over all vdim entries (plain frequencies of rot_base)
+    out_scale: float = 1.0          # factor on the mixer's output (its weight in a sum of mixers)
 
     @property
     def cache_width(self) -> int:
         return self.kv_heads * (self.dim + self.vdim)
+
+    @property
+    def rot_key(self):
+        """Key of the step's angle tables for queries and keys (TokenInferState.rotary)."""
+        return (self.rot_base, self.rot_dims) if self.rot_scaling is None else (self.rot_base, self.rot_dims, self.rot_scaling)
+
+    @property
+    def vrot_key(self):
+        return (self.rot_base, self.vdim) if self.value_rotation else None
+
+
+@dataclasses.dataclass(frozen=True)
+class LinearAttentionSpec:
+    """Linear attention with a constant decay per head: S <- decay_h S + k v^T (dim x vdim per head, fp32, one per sequence),
+    out = S^T q, with q, k, v = silu(projection); the heads' outputs are RMS-normed together (weight `norm`), gated by
+    sigmoid(projection `g`) and projected."""
+    heads: int
+    dim: int
+    vdim: int
+    decay: tuple
+    out_scale: float = 1.0
+
+
+@dataclasses.dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Two mixers that read the same input; the result is left.out_scale * left + right.out_scale * right."""
+    left: WindowAttentionSpec
+    right: LinearAttentionSpec
+
+    # the cache geometry is the attention's
+    @property
+    def kv_from(self):
+        return self.left.kv_from
+
+    @property
+    def cache_width(self) -> int:
+        return self.left.cache_width
+
+
+@dataclasses.dataclass(frozen=True)
+class GatedRecurrenceSpec:
+    """A real-gated linear recurrent unit behind a causal convolution per channel, times a GELU branch: `width` channels whose
+    two gates are block-diagonal projections (`blocks` blocks) of the convolution's output; `conv` taps.  No cache rows: the
+    state (fp32 [width]) and the convolution's last conv - 1 inputs live per sequence."""
+    width: int
+    blocks: int
+    conv: int
+    kv_from: Optional[int] = None
+    cache_width: int = 0            # no rows in the paged cache
 
 
 @dataclasses.dataclass(frozen=True)
@@ -112,10 +170,12 @@ class FeedForwardSpec:
     ff: int                     # hidden size of the dense layer / of ONE expert
     experts: int = 0
     top: int = 0
-    activation: str = "relu2"   # "relu2": relu(up)^2 | "clamped_glu": min(gate, limit) * sigmoid(1.702 .) * (clamp(up) + 1)
+    # "relu2": relu(up)^2 | "clamped_glu": min(gate, limit) * sigmoid(1.702 .) * (clamp(up) + 1) | "silu_glu": silu(gate) * up
+    activation: str = "relu2"
     limit: float = 0.0          # clamped_glu: bound of the gate (above) and of the up projection (both sides)
     # routing.  "top_softmax": softmax over the `top` largest logits.  "softmax_grouped": scores are a softmax over all experts,
     # only experts of the `keep` best of `groups` groups can be chosen, the chosen scores are renormalised and scaled.
+    # "sigmoid_bias": scores are sigmoids; the `top` largest score + bias (tensor `correction`) are chosen; weights are the scores.
     routing: str = "top_softmax"
     groups: int = 1
     keep: int = 1
@@ -129,7 +189,9 @@ def _cache_geometry(mixers):
     -> (layer -> (row width, slot within that width's tensor), row width -> number of slots)."""
     cache_slot, slots_per_width = {}, {}
     for i, s in enumerate(mixers):
-        if s.kv_from is None:
+        if s.cache_width == 0:
+            cache_slot[i] = None                # a mixer without cache rows (recurrent state only)
+        elif s.kv_from is None:
             n = slots_per_width.get(s.cache_width, 0)
             cache_slot[i] = (s.cache_width, n)
             slots_per_width[s.cache_width] = n + 1
@@ -247,3 +309,92 @@ class RivudraModelConfig:
     def load_from_model_path(model_path: str) -> "RivudraModelConfig":
         with open(os.path.join(model_path, "config.json"), "r", encoding="utf-8") as f:
             return RivudraModelConfig(json.load(f))
+
+
+# ---------------------------------------------------------------- Buzarax
+@dataclasses.dataclass(frozen=True)
+class PairHashSpec:
+    """A second embedding table indexed by a hash of (previous token, token): row (previous * mul_prev + token * mul_cur) mod
+    buckets; the table's extra last row (number `buckets`) is the one of a sequence's first token."""
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+
+
+class BuzaraxModelConfig:
+    """config.json of the Buzarax design: {"architecture": "Buzarax", "vocab", "width", "norm": {"eps"}, "logit_softcap",
+    "embedding": {"bigram": {"buckets", "mul_prev", "mul_cur"}}, "layers": [{"type": "parallel" | "rglru", "mixer": {...},
+    "mlp": {"kind": "dense", "ff", "limit"} | {"kind": "moe", "router": {"experts", "top"}, "expert": {"ff"}} | null}, ...]}.
+    "parallel": {"left": {"heads", "kv_heads", "dim", "vdim", "scale", "softcap", "rot": {"base", "dims", "scaling": {"factor",
+    "original", "fast", "slow"}}}, "right": {"heads", "dim", "vdim", "decay": [...]}, "left_scale", "right_scale"};
+    "rglru": {"width", "blocks", "conv"}.  Layers are sequential blocks whose sublayers read the residual stream itself and
+    whose outputs are normalised (one scalar gain) before they are added; after every layer the stream is a learned weighted
+    sum of all earlier results (tensor `dwa`).  Every size may differ from layer to layer."""
+    family = "buzarax"
+
+    def __init__(self, model_config: dict):
+        assert model_config.get("architecture") == "Buzarax", f"not a Buzarax config: {model_config.get('architecture')!r}"
+        self.raw = dict(model_config)
+        self.vocab_size = int(model_config["vocab"])
+        self.hidden_size = int(model_config["width"])
+        self.rms_norm_eps = float(model_config["norm"]["eps"])
+        self.logit_softcap = float(model_config.get("logit_softcap") or 0.0)
+        pair = (model_config.get("embedding") or {}).get("bigram")
+        self.pair_hash = PairHashSpec(int(pair["buckets"]), int(pair["mul_prev"]), int(pair["mul_cur"])) if pair else None
+        self.mixers, self.ffs = [], []
+        for i, layer in enumerate(model_config["layers"]):
+            m = layer["mixer"]
+            if layer["type"] == "rglru":
+                spec = GatedRecurrenceSpec(width=int(m["width"]), blocks=int(m["blocks"]), conv=int(m["conv"]))
+                assert spec.width % spec.blocks == 0 and 1 <= spec.conv <= 8, f"layer {i}: width must split into blocks; 1 <= conv <= 8"
+            else:
+                assert layer["type"] == "parallel", f"layer {i}: unknown mixer type {layer['type']!r}"
+                a, b = m["left"], m["right"]
+                rot = a.get("rot") or {}
+                sc = rot.get("scaling")
+                left = WindowAttentionSpec(
+                    heads=int(a["heads"]), kv_heads=int(a.get("kv_heads") or a["heads"]), dim=int(a["dim"]), vdim=int(a["vdim"]),
+                    window=0, rot_base=float(rot.get("base", 10000.0)), rot_dims=int(rot.get("dims", 0)), scale=float(a["scale"]),
+                    sink=True, gate=False, pair_halves=True,
+                    rot_scaling=(float(sc["factor"]), float(sc["original"]), float(sc["fast"]), float(sc["slow"])) if sc else None,
+                    qk_unit_norm=True, softcap=float(a.get("softcap") or 0.0), value_rotation=True,
+                    out_scale=float(m.get("left_scale", 1.0)))
+                assert left.heads % left.kv_heads == 0, f"layer {i}: heads must be a multiple of kv_heads"
+                assert left.rot_dims % 2 == 0 and left.rot_dims <= left.dim and left.vdim % 2 == 0, \
+                    f"layer {i}: rot.dims must be even and <= dim, vdim even"
+                right = LinearAttentionSpec(heads=int(b["heads"]), dim=int(b["dim"]), vdim=int(b["vdim"]),
+                                            decay=tuple(float(d) for d in b["decay"]), out_scale=float(m.get("right_scale", 1.0)))
+                assert len(right.decay) == right.heads, f"layer {i}: one decay per head"
+                spec = ParallelMixerSpec(left, right)
+            self.mixers.append(spec)
+            f = layer.get("mlp")
+            if f is None:
+                self.ffs.append(None)
+            elif f["kind"] == "dense":
+                self.ffs.append(FeedForwardSpec("dense", int(f["ff"]), activation="clamped_glu", limit=float(f["limit"])))
+            else:
+                assert f["kind"] == "moe", f"layer {i}: unknown mlp kind {f['kind']!r}"
+                self.ffs.append(FeedForwardSpec("moe", int(f["expert"]["ff"]), int(f["router"]["experts"]), int(f["router"]["top"]),
+                                                activation="silu_glu", routing="sigmoid_bias"))
+                assert self.ffs[-1].top <= self.ffs[-1].experts, f"layer {i}: top > experts"
+        self.num_layers = len(self.mixers)
+        self.cache_slot, self.cache_slots_per_width = _cache_geometry(self.mixers)
+
+    def get_kvslot_size(self, dtype: torch.dtype = torch.bfloat16) -> int:
+        """Bytes of cache one token occupies: one [keys | values] row per attention layer (recurrent layers hold none)."""
+        return sum(w * n for w, n in self.cache_slots_per_width.items()) * dtype.itemsize
+
+    def get_state_size(self, dtype: torch.dtype = torch.bfloat16) -> int:
+        """Bytes of recurrent state one SEQUENCE occupies, whatever its length."""
+        n = 4 if self.pair_hash else 0
+        for s in self.mixers:
+            if isinstance(s, GatedRecurrenceSpec):
+                n += 4 * s.width + (s.conv - 1) * s.width * dtype.itemsize
+            else:
+                n += 4 * s.right.heads * s.right.dim * s.right.vdim
+        return n
+
+    @staticmethod
+    def load_from_model_path(model_path: str) -> "BuzaraxModelConfig":
+        with open(os.path.join(model_path, "config.json"), "r", encoding="utf-8") as f:
+            return BuzaraxModelConfig(json.load(f))

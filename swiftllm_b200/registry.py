@@ -4,6 +4,7 @@
     llama       "model_type": "llama"                       LlamaModelConfig       worker.model.LlamaModel
     bupozen     "architecture": "Bupozen"                   BupozenModelConfig     worker.bupozen_model.BupozenModel
     rivudra     "architecture": "Rivudra"                   RivudraModelConfig     worker.rivudra_model.RivudraModel
+    buzarax     "architecture": "Buzarax"                   BuzaraxModelConfig     worker.buzarax_model.BuzaraxModel
 
 Every worker class has the same public surface (load_weights, profile_num_blocks, init_kvcache_and_swap, forward /
 forward_async with the prefill-chunks-then-decodes batch layout, free_seqs_resources), so schedulers, examples and
@@ -23,6 +24,8 @@ _FAMILIES = {
                 "swiftllm_b200.model_config:BupozenModelConfig", "swiftllm_b200.worker.bupozen_model:BupozenModel"),
     "rivudra": (lambda raw: raw.get("architecture") == "Rivudra",
                 "swiftllm_b200.model_config:RivudraModelConfig", "swiftllm_b200.worker.rivudra_model:RivudraModel"),
+    "buzarax": (lambda raw: raw.get("architecture") == "Buzarax",
+                "swiftllm_b200.model_config:BuzaraxModelConfig", "swiftllm_b200.worker.buzarax_model:BuzaraxModel"),
 }
 
 

@@ -66,5 +66,7 @@ class TokenInferState:
     token_positions: torch.Tensor                   # [num_tokens] position of every token within its sequence
     output_rows: torch.Tensor                       # rows whose logits are computed: the last row of every sequence, then extras
     ignore_kvcache: bool = False                    # memory-profiling forward: no cache store, no attention
-    # rotary angle tables of the step, keyed by (base, dims): (cos, sin) fp32 [num_tokens, dims / 2]
+    # rotary angle tables of the step, keyed by (base, dims[, scaling]): (cos, sin) fp32 [num_tokens, dims / 2]
     rotary: dict = dataclasses.field(default_factory=dict)
+    # [batch_size + 1] first row of every sequence of the step, closed with num_tokens (kernels that walk a sequence's rows)
+    seg_starts: Optional[torch.Tensor] = None

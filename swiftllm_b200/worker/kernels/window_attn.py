@@ -1,8 +1,23 @@
 """Gated sliding-window attention with grouped key/value heads over the paged cache (csrc/window_attn.cu).  Cache layout
-[num_blocks, slots, block_size, G * (dk + dv)]: per token and layer ONE row [rotated keys of all G heads | their values]."""
+[num_blocks, slots, block_size, G * (dk + dv)]: per token and layer ONE row [rotated keys of all G heads | their values].
+
+Options (`AttnOptions`) that other designs switch on: rotary pairs as halves instead of neighbours, unit-RMS queries and keys, a
+tanh cap on the scores, values that are stored turned by their position (the output is turned back), a factor on the output."""
+import dataclasses
 import torch
 
 from swiftllm_b200 import _lib
+
+
+@dataclasses.dataclass(frozen=True)
+class AttnOptions:
+    pair_halves: bool = False       # rotary pairs (i, i + rot_dims / 2) instead of (2i, 2i + 1)
+    qk_norm_eps: float = -1.0       # >= 0: rotated queries / keys are divided by sqrt(mean of squares over the head + eps)
+    softcap: float = 0.0            # > 0: score <- softcap * tanh(score / softcap)
+    out_scale: float = 1.0
+
+
+PLAIN = AttnOptions()
 
 
 def _stride0(x: torch.Tensor) -> int:
@@ -10,8 +25,10 @@ def _stride0(x: torch.Tensor) -> int:
 
 
 def window_kv_store(k: torch.Tensor, v: torch.Tensor, cache: torch.Tensor, slot: int, block_table: torch.Tensor, infer_state,
-                    kv_heads: int, dk: int, dv: int, rot_dims: int, cos: torch.Tensor, sin: torch.Tensor):
-    """k [T, G * dk], v [T, G * dv] (row-strided slices are fine): rotate the keys, write the tokens' cache rows."""
+                    kv_heads: int, dk: int, dv: int, rot_dims: int, cos: torch.Tensor, sin: torch.Tensor,
+                    opt: AttnOptions = PLAIN, vcos: torch.Tensor = None, vsin: torch.Tensor = None):
+    """k [T, G * dk], v [T, G * dv] (row-strided slices are fine): rotate the keys, write the tokens' cache rows.
+    vcos / vsin fp32 [T, dv / 2]: the values are stored turned by their position."""
     T = k.shape[0]
     assert k.dim() == 2 and k.stride(1) == 1 and v.stride(1) == 1 and k.shape[1] == kv_heads * dk and v.shape == (T, kv_heads * dv)
     assert cache.is_contiguous() and cache.dtype == k.dtype == v.dtype and cache.shape[3] == kv_heads * (dk + dv)
@@ -19,12 +36,14 @@ def window_kv_store(k: torch.Tensor, v: torch.Tensor, cache: torch.Tensor, slot:
     _lib.check(_lib.lib().sllm_window_kv_store(
         k.data_ptr(), _stride0(k), v.data_ptr(), _stride0(v), _lib.ptr(cos), _lib.ptr(sin), infer_state.token_seq_ids.data_ptr(),
         infer_state.token_positions.data_ptr(), block_table.data_ptr(), block_table.shape[1], cache.data_ptr(), cache.shape[1],
-        slot, cache.shape[2], T, kv_heads, dk, dv, rot_dims, _lib.dtype_tag_f32(k.dtype), _lib.stream()), "window_kv_store")
+        slot, cache.shape[2], T, kv_heads, dk, dv, rot_dims, 1 if opt.pair_halves else 0, opt.qk_norm_eps, _lib.ptr(vcos),
+        _lib.ptr(vsin), _lib.dtype_tag_f32(k.dtype), _lib.stream()), "window_kv_store")
 
 
 def window_attention(q: torch.Tensor, gate, cache: torch.Tensor, slot: int, block_table: torch.Tensor, infer_state,
                      out: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int, rot_dims: int, window: int, scale: float,
-                     sink: bool, cos: torch.Tensor, sin: torch.Tensor):
+                     sink: bool, cos: torch.Tensor, sin: torch.Tensor, opt: AttnOptions = PLAIN, vcos: torch.Tensor = None,
+                     vsin: torch.Tensor = None):
     """q [T, H * dk] (un-rotated), gate [T, H * dv] logits or None, out [T, H * dv]; row-strided slices are fine."""
     T = q.shape[0]
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.shape == (T, heads * dk) and out.shape == (T, heads * dv)
@@ -35,7 +54,9 @@ def window_attention(q: torch.Tensor, gate, cache: torch.Tensor, slot: int, bloc
         q.data_ptr(), _stride0(q), _lib.ptr(cos), _lib.ptr(sin), _lib.ptr(gate), _stride0(gate) if gate is not None else 0,
         cache.data_ptr(), cache.shape[1], slot, cache.shape[2], block_table.data_ptr(), block_table.shape[1],
         infer_state.token_seq_ids.data_ptr(), infer_state.token_positions.data_ptr(), out.data_ptr(), _stride0(out), T,
-        min(T, max(0, int(getattr(infer_state, "num_prefill_tokens", T)))), heads, kv_heads, dk, dv, rot_dims, window, scale, 1 if sink else 0, _lib.dtype_tag_f32(q.dtype), _lib.stream()),
+        min(T, max(0, int(getattr(infer_state, "num_prefill_tokens", T)))), heads, kv_heads, dk, dv, rot_dims, window, scale, 1 if sink else 0,
+        1 if opt.pair_halves else 0, opt.qk_norm_eps, opt.softcap, _lib.ptr(vcos), _lib.ptr(vsin), opt.out_scale,
+        _lib.dtype_tag_f32(q.dtype), _lib.stream()),
         "window_attention")
 
 

@@ -1,30 +1,51 @@
-"""Gated sliding-window attention mixer with grouped key/value heads: ONE fused GEMM [q ; k ; v ; gate] on the block's normed
-input -> (rotary of k + cache store, one kernel) -> attention over the paged cache (rotary of q, window, softmax with an
-optional sink, sigmoid output gate: one kernel) -> o GEMM."""
+"""Softmax attention mixer with grouped key/value heads over the paged cache: ONE fused GEMM [q ; k ; v (; gate)] on the block's
+input -> (rotary of k + cache store, one kernel) -> attention (rotary of q, window, softmax with an optional sink, optional
+sigmoid output gate: one kernel) -> o GEMM.  The specification's options (model_config.WindowAttentionSpec: rotary pairs as
+halves, stretched frequencies, unit-RMS queries and keys, capped scores, values turned by their position) go to the same two
+kernels.  `attend` is the part between the two GEMMs, for mixers that fuse their projections with a neighbour's."""
 import torch
 
 from swiftllm_b200.worker.kernels.linear import linear
-from swiftllm_b200.worker.kernels.window_attn import window_attention, window_kv_store
+from swiftllm_b200.worker.kernels.window_attn import AttnOptions, window_attention, window_kv_store
 
 
 class WindowAttentionMixer:
     def __init__(self, spec, weight, eps: float, cache_key):
         self.spec, self.weight = spec, weight
         self.cache_width, self.cache_slot = cache_key          # which cache tensor and which of its slots this layer uses
+        self.options = AttnOptions(pair_halves=spec.pair_halves, qk_norm_eps=eps if spec.qk_unit_norm else -1.0,
+                                   softcap=spec.softcap, out_scale=spec.out_scale)
+
+    def register(self, model):
+        m = self.spec
+        model._register_rotary(m.rot_key, m.rot_base, m.rot_dims, m.rot_scaling)
+        if m.value_rotation:
+            model._register_rotary(m.vrot_key, m.rot_base, m.vdim)
+
+    @property
+    def proj_widths(self):
+        """Columns of the fused input projection: q, k, v (, gate)."""
+        m = self.spec
+        return [m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim] + ([m.heads * m.vdim] if m.gate else [])
+
+    def attend(self, q, k, v, gate, out, caches: dict, block_table, st):
+        """q [T, H dk], k [T, G dk], v [T, G dv], gate [T, H dv] or None (column slices of a wider matrix are fine) -> out [T, H dv]."""
+        m = self.spec
+        if st.ignore_kvcache:
+            out.zero_()
+            return
+        cos, sin = st.rotary[m.rot_key] if m.rot_dims > 0 else (None, None)
+        vcos, vsin = st.rotary[m.vrot_key] if m.value_rotation else (None, None)
+        cache = caches[self.cache_width]
+        window_kv_store(k, v, cache, self.cache_slot, block_table, st, m.kv_heads, m.dim, m.vdim, m.rot_dims, cos, sin,
+                        self.options, vcos, vsin)
+        window_attention(q, gate, cache, self.cache_slot, block_table, st, out, m.heads, m.kv_heads, m.dim, m.vdim,
+                         m.rot_dims, m.window, m.scale, m.sink, cos, sin, self.options, vcos, vsin)
 
     def forward(self, h: torch.Tensor, caches: dict, block_table: torch.Tensor, st) -> torch.Tensor:
         m, w = self.spec, self.weight
-        T, H, G, dk, dv = h.shape[0], m.heads, m.kv_heads, m.dim, m.vdim
-        proj = linear(h, w.in_proj)                             # [T, H dk | G dk | G dv | H dv]
-        q_end, k_end, v_end = H * dk, (H + G) * dk, (H + G) * dk + G * dv
-        out = torch.empty((T, H * dv), dtype=h.dtype, device=h.device)
-        if st.ignore_kvcache:
-            out.zero_()
-        else:
-            cos, sin = st.rotary[(m.rot_base, m.rot_dims)] if m.rot_dims > 0 else (None, None)
-            cache = caches[self.cache_width]
-            window_kv_store(proj[:, q_end:k_end], proj[:, k_end:v_end], cache, self.cache_slot, block_table, st, G, dk, dv,
-                            m.rot_dims, cos, sin)
-            window_attention(proj[:, :q_end], proj[:, v_end:], cache, self.cache_slot, block_table, st, out, H, G, dk, dv,
-                             m.rot_dims, m.window, m.scale, m.sink, cos, sin)
+        proj = linear(h, w.in_proj)                             # [T, H dk | G dk | G dv (| H dv)]
+        parts = list(torch.split(proj, self.proj_widths, dim=1)) + [None]
+        out = torch.empty((h.shape[0], m.heads * m.vdim), dtype=h.dtype, device=h.device)
+        self.attend(parts[0], parts[1], parts[2], parts[3], out, caches, block_table, st)
         return linear(out, w.o)

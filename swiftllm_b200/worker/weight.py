@@ -219,6 +219,98 @@ def load_rivudra_weights(model_config, dtype: torch.dtype, model_path: Optional[
     return weight
 
 
+class BuzaraxLayerWeight:
+    """One sequential block.  Checkpoint names: `l<i>.norm1`, `l<i>.norm2` (scalars), `l<i>.dwa` ([i + 2]), and
+    mixer "parallel": `l<i>.mix.left.{q, k, v, o}`, `l<i>.mix.right.{q, k, v, g, o, norm}`;
+    mixer "rglru": `l<i>.mix.{y, y.b, x, x.b, conv, conv.b, ra, ra.b, ri, ri.b, lam, o}`;
+    feed-forward: `l<i>.mlp.{gate, up, down}` or `l<i>.mlp.{router, correction, e<k>.{gate, up, down}}`.
+    Fusions made at load time: every projection that reads the block's input is one GEMM operand (`in_proj`: [left q ; k ; v ;
+    right q ; k ; v ; g], or [y ; x] with `in_bias`); the two output projections of a parallel mixer are one operand side by side
+    (`o`; the mixers' weights in the sum are applied by the kernels that write its input); the two block-diagonal gate
+    projections are one batched operand (`gate_w` [blocks, in, 2 * out], `gate_b`); `rate` = -8 softplus(lam) in fp32; the
+    experts' [gate ; up] rows and down columns are concatenated expert by expert.  Scalars, `dwa`, the group norm, the router
+    and its correction are fp32."""
+
+    def __init__(self, layer_id: int, model_config, dtype: torch.dtype):
+        self.layer_id, self.model_config, self.dtype = layer_id, model_config, dtype
+
+    def load_weights(self, getter: Callable, device):
+        from swiftllm_b200.model_config import GatedRecurrenceSpec
+        c, i = self.model_config, self.layer_id
+        m, f, W = c.mixers[i], c.ffs[i], c.hidden_size
+
+        def get(name, shape, dtype=None):
+            w = getter(f"l{i}.{name}", shape, dtype or self.dtype)
+            assert isinstance(w, torch.Tensor) and tuple(w.shape) == tuple(shape), f"l{i}.{name}: expected shape {tuple(shape)}"
+            return w.to(device=device, dtype=dtype or self.dtype).contiguous()
+
+        self.norm1 = get("norm1", (), torch.float32).reshape(1)
+        self.dwa = get("dwa", (i + 2,), torch.float32)
+        if isinstance(m, GatedRecurrenceSpec):
+            C, B, K = m.width, m.blocks, m.conv
+            cb = C // B
+            self.in_proj = torch.cat([get("mix.y", (C, W)), get("mix.x", (C, W))], dim=0).contiguous()
+            self.in_bias = torch.cat([get("mix.y.b", (C,)), get("mix.x.b", (C,))], dim=0).contiguous()
+            self.conv, self.conv_b = get("mix.conv", (C, K)), get("mix.conv.b", (C,))
+            gw = torch.cat([get("mix.ra", (B, cb, cb)), get("mix.ri", (B, cb, cb))], dim=1)          # [B, 2 cb (out), cb (in)]
+            self.gate_w = gw.transpose(1, 2).contiguous()                                               # [B, in, 2 out]
+            self.gate_b = torch.cat([get("mix.ra.b", (B, cb)), get("mix.ri.b", (B, cb))], dim=1).reshape(B, 1, 2 * cb).contiguous()
+            self.rate = (-8.0 * torch.nn.functional.softplus(get("mix.lam", (C,), torch.float32))).contiguous()
+            self.o = get("mix.o", (W, C))
+        else:
+            a, b = m.left, m.right
+            self.in_proj = torch.cat([
+                get("mix.left.q", (a.heads * a.dim, W)), get("mix.left.k", (a.kv_heads * a.dim, W)),
+                get("mix.left.v", (a.kv_heads * a.vdim, W)), get("mix.right.q", (b.heads * b.dim, W)),
+                get("mix.right.k", (b.heads * b.dim, W)), get("mix.right.v", (b.heads * b.vdim, W)),
+                get("mix.right.g", (b.heads * b.vdim, W))], dim=0).contiguous()
+            self.o = torch.cat([get("mix.left.o", (W, a.heads * a.vdim)), get("mix.right.o", (W, b.heads * b.vdim))], dim=1).contiguous()
+            self.lin_norm = get("mix.right.norm", (b.heads * b.vdim,), torch.float32)
+            self.decay = torch.tensor(b.decay, dtype=torch.float32).to(device)
+        if f is None:
+            return
+        self.norm2 = get("norm2", (), torch.float32).reshape(1)
+        if f.kind == "dense":
+            self.up = torch.cat([get("mlp.gate", (f.ff, W)), get("mlp.up", (f.ff, W))], dim=0).contiguous()
+            self.down = get("mlp.down", (W, f.ff))
+        else:
+            self.router = get("mlp.router", (f.experts, W), torch.float32)                            # the router runs in fp32
+            self.correction = get("mlp.correction", (f.experts,), torch.float32)
+            self.up = torch.cat([get(f"mlp.e{e}.{part}", (f.ff, W)) for e in range(f.experts) for part in ("gate", "up")],
+                                dim=0).contiguous()
+            self.down = torch.cat([get(f"mlp.e{e}.down", (W, f.ff)) for e in range(f.experts)], dim=1).contiguous()
+
+
+class BuzaraxWeight:
+    def __init__(self, model_config, dtype: torch.dtype):
+        self.model_config, self.dtype = model_config, dtype
+        self.layers = [BuzaraxLayerWeight(i, model_config, dtype) for i in range(model_config.num_layers)]
+
+    def load_weights(self, getter: Callable, device="cuda"):
+        c = self.model_config
+        vs = (c.vocab_size, c.hidden_size)
+        self.wte = getter("embed", vs, self.dtype).to(device=device, dtype=self.dtype).contiguous()
+        self.pairs = None
+        if c.pair_hash is not None:
+            self.pairs = getter("bigram", (c.pair_hash.buckets + 1, c.hidden_size), self.dtype).to(device=device, dtype=self.dtype).contiguous()
+        # the final norm has ONE gain: kept as an fp32 vector of equal entries, the form the fused add + norm kernel reads
+        g = getter("final.norm", (), torch.float32).to(device=device, dtype=torch.float32)
+        self.final_norm = g.reshape(1).expand(c.hidden_size).contiguous()
+        self.lm_head = getter("head", vs, self.dtype).to(device=device, dtype=self.dtype).contiguous()
+        self.lm_head_sharded = False
+        for layer in self.layers:
+            layer.load_weights(getter, device)
+
+
+def load_buzarax_weights(model_config, dtype: torch.dtype, model_path: Optional[str], use_dummy: bool = False,
+                         getter: Optional[Callable] = None, device="cuda") -> BuzaraxWeight:
+    if getter is None:
+        getter = dummy_getter(device) if use_dummy else checkpoint_getter(model_path, device)
+    weight = BuzaraxWeight(model_config, dtype)
+    weight.load_weights(getter, device)
+    return weight
+
+
 # ---------------------------------------------------------------- getters
 def dummy_getter(device="cuda"):
     """weight.py:215-218: uniform(-1e-3, 1e-3), unseeded ("mainly for profiling")."""

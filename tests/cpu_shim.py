@@ -232,17 +232,48 @@ def _moe_clamped_glu_scale(u, weights, experts, ff, limit, shared_ff, shared_lim
     return torch.cat(parts, dim=1).to(u.dtype)
 
 
-def _window_kv_store(k, v, cache, slot, block_table, st, kv_heads, dk, dv, rot_dims, cos, sin):
+def _rot_any(v, cos, sin, rot_dims, halves):
+    """v [T, ..., d] fp32; halves: pairs (i, i + rot_dims/2), else (2i, 2i+1)."""
+    if not halves:
+        return _rot_pairs(v, cos, sin, rot_dims)
+    if rot_dims == 0:
+        return v
+    hf = rot_dims // 2
+    shape = (v.shape[0],) + (1,) * (v.dim() - 2) + (hf,)
+    c, s = cos.view(shape), sin.view(shape)
+    u, w = v[..., :hf], v[..., hf:rot_dims]
+    out = v.clone()
+    out[..., :hf] = u * c - w * s
+    out[..., hf:rot_dims] = w * c + u * s
+    return out
+
+
+def _unit_rms(x, eps):
+    return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+
+
+def _window_kv_store(k, v, cache, slot, block_table, st, kv_heads, dk, dv, rot_dims, cos, sin, opt=None, vcos=None, vsin=None):
     T = k.shape[0]
-    kr = _rot_pairs(k.float().view(T, kv_heads, dk), cos, sin, rot_dims).reshape(T, kv_heads * dk).to(k.dtype)
+    halves = bool(opt and opt.pair_halves)
+    kr = _rot_any(k.float().view(T, kv_heads, dk), cos, sin, rot_dims, halves)
+    if opt and opt.qk_norm_eps >= 0:
+        kr = _unit_rms(kr, opt.qk_norm_eps)
+    kr = kr.reshape(T, kv_heads * dk).to(k.dtype)
+    if vcos is not None:
+        v = _rot_any(v.float().view(T, kv_heads, dv), vcos, vsin, dv, halves).reshape(T, kv_heads * dv).to(k.dtype)
     bs = cache.shape[2]
     for t, (sq, p) in enumerate(zip(st.token_seq_ids.tolist(), st.token_positions.tolist())):
         cache[int(block_table[sq, p // bs]), slot, p % bs] = torch.cat([kr[t], v[t]])
 
 
-def _window_attention(q, gate, cache, slot, block_table, st, out, heads, kv_heads, dk, dv, rot_dims, window, scale, sink, cos, sin):
+def _window_attention(q, gate, cache, slot, block_table, st, out, heads, kv_heads, dk, dv, rot_dims, window, scale, sink, cos, sin,
+                      opt=None, vcos=None, vsin=None):
     T = q.shape[0]
-    qa = _rot_pairs(q.float().view(T, heads, dk), cos, sin, rot_dims) * scale
+    halves = bool(opt and opt.pair_halves)
+    qa = _rot_any(q.float().view(T, heads, dk), cos, sin, rot_dims, halves)
+    if opt and opt.qk_norm_eps >= 0:
+        qa = _unit_rms(qa, opt.qk_norm_eps)
+    qa = qa * scale
     rep = heads // kv_heads
     for t, (sq, p) in enumerate(zip(st.token_seq_ids.tolist(), st.token_positions.tolist())):
         lo = max(0, p - window + 1) if window > 0 else 0
@@ -250,13 +281,129 @@ def _window_attention(q, gate, cache, slot, block_table, st, out, heads, kv_head
         ks = rows[:, :kv_heads * dk].view(-1, kv_heads, dk).repeat_interleave(rep, dim=1)     # [n, H, dk]
         vs = rows[:, kv_heads * dk:].view(-1, kv_heads, dv).repeat_interleave(rep, dim=1)
         sc = torch.einsum("hd,nhd->hn", qa[t], ks)
+        if opt and opt.softcap > 0:
+            sc = opt.softcap * torch.tanh(sc / opt.softcap)
         if sink:
             sc = torch.cat([sc, torch.zeros(heads, 1)], dim=1)
         pr = torch.softmax(sc, dim=-1)[:, :rows.shape[0]]
-        o = torch.einsum("hn,nhd->hd", pr, vs).reshape(heads * dv)
+        o = torch.einsum("hn,nhd->hd", pr, vs)
+        if vcos is not None:
+            o = _rot_any(o[None], vcos[t:t + 1], -vsin[t:t + 1], dv, halves)[0]
+        o = o.reshape(heads * dv) * (opt.out_scale if opt else 1.0)
         if gate is not None:
             o = o * torch.sigmoid(gate[t].float())
         out[t] = o.to(out.dtype)
+
+
+# ---------------------------------------------------------------- stand-ins of the sequential-block / recurrent kernels
+def _segments(st):
+    s = st.seg_starts.tolist()
+    return [(sq, s[b], s[b + 1]) for b, sq in enumerate(st.seq_ids.tolist()) if s[b + 1] > s[b]]
+
+
+def _embed_pair_hash(tokens, st, last_token, embed, pairs, buckets, mul_prev, mul_cur, x_copy=None):
+    x = embed[tokens.long()].float()
+    if pairs is not None:
+        pos = st.token_positions.tolist()
+        toks = tokens.tolist()
+        for sq, lo, hi in _segments(st):
+            for t in range(lo, hi):
+                if pos[t] == 0:
+                    row = buckets
+                else:
+                    prev = toks[t - 1] if t > lo else int(last_token[sq])
+                    row = (prev * mul_prev + toks[t] * mul_cur) % buckets
+                x[t] += pairs[row].float()
+            last_token[sq] = toks[hi - 1]
+    if x_copy is not None:
+        x_copy.copy_(x)
+    return x, x.to(embed.dtype)
+
+
+def _postnorm_add_mix(x, y, gain, eps, h, history=None, slot=0, mix=None):
+    if y is not None:
+        x += _unit_rms(y.float(), eps) * gain
+    if history is not None:
+        history[slot] = x
+    if mix is not None:
+        x.copy_(sum(mix[j] * history[j] for j in range(slot + 1)))
+    h.copy_(x.to(h.dtype))
+
+
+def _tanh_cap_inplace(x, cap):
+    x.copy_(cap * torch.tanh(x / cap))
+
+
+def _moe_route_sigmoid(logits, bias, top):
+    s = torch.sigmoid(logits)
+    idx = torch.topk(s + (bias if bias is not None else 0.0), top, dim=-1).indices
+    return torch.zeros_like(s).scatter_(1, idx, s.gather(1, idx))
+
+
+def _moe_silu_glu_scale(u, weights, experts, ff):
+    T = u.shape[0]
+    b = u.float().view(T, experts, 2 * ff)
+    g, v = b[..., :ff], b[..., ff:]
+    return (g * torch.sigmoid(g) * v * weights[:, :, None]).reshape(T, experts * ff).to(u.dtype)
+
+
+def _causal_conv(xin, w, bias, tail, st):
+    T, C = xin.shape
+    K = w.shape[1]
+    u = torch.zeros(T, C)
+    pos = st.token_positions.tolist()
+    for sq, lo, hi in _segments(st):
+        before = tail[sq].float() if (K > 1 and pos[lo] > 0) else torch.zeros(K - 1, C)
+        seq = torch.cat([before, xin[lo:hi].float()])                         # row K-1 + i: the segment's token i
+        for i in range(hi - lo):
+            u[lo + i] = (bias.float() if bias is not None else 0.0) + (seq[i:i + K] * w.float().T).sum(0)
+    return u.to(xin.dtype)
+
+
+def _rglru_scan(u, gates, ybr, rate, xin, state, tail, st):
+    T, C = u.shape
+    blocks, K = gates.shape[0], tail.shape[1] + 1
+    cb = C // blocks
+    g = gates.float()
+    r = torch.sigmoid(g[:, :, :cb]).transpose(0, 1).reshape(T, C)
+    ig = torch.sigmoid(g[:, :, cb:]).transpose(0, 1).reshape(T, C)
+    a = torch.exp(rate * r)
+    y = ybr.float()
+    gelu = 0.5 * y * (1.0 + torch.tanh(0.7978845608028654 * (y + 0.044715 * y ** 3)))
+    out = torch.zeros(T, C)
+    pos = st.token_positions.tolist()
+    for sq, lo, hi in _segments(st):
+        S = state[sq].clone() if pos[lo] > 0 else torch.zeros(C)
+        for t in range(lo, hi):
+            S = a[t] * S + torch.sqrt(torch.clamp(1.0 - a[t] * a[t], min=0.0)) * (ig[t] * u[t].float())
+            out[t] = S * gelu[t]
+        state[sq] = S
+        if K > 1:
+            before = tail[sq].float() if pos[lo] > 0 else torch.zeros(K - 1, C)
+            tail[sq] = torch.cat([before, xin[lo:hi].float()])[-(K - 1):].to(tail.dtype)
+    return out.to(u.dtype)
+
+
+def _linear_attention(q, k, v, decay, state, st, heads, dk, dv):
+    T = q.shape[0]
+    silu = torch.nn.functional.silu
+    qf, kf, vf = silu(q.float()).view(T, heads, dk), silu(k.float()).view(T, heads, dk), silu(v.float()).view(T, heads, dv)
+    out = torch.zeros(T, heads, dv)
+    pos = st.token_positions.tolist()
+    for sq, lo, hi in _segments(st):
+        S = state[sq].clone() if pos[lo] > 0 else torch.zeros(heads, dk, dv)
+        for t in range(lo, hi):
+            S = decay[:, None, None] * S + kf[t][:, :, None] * vf[t][:, None, :]
+            out[t] = torch.einsum("hkv,hk->hv", S, qf[t])
+        state[sq] = S
+    return out.reshape(T, heads * dv)
+
+
+def _gated_rmsnorm(x, weight, gate, eps, out, out_scale=1.0):
+    y = _unit_rms(x, eps) * weight * out_scale
+    if gate is not None:
+        y = y * torch.sigmoid(gate.float())
+    out.copy_(y.to(out.dtype))
 
 
 class GlooFusedAllReduce:
@@ -329,6 +476,16 @@ _PATCHES = [
     ("swiftllm_b200.worker.layers.latent_attention", "latent_kv_store", _latent_kv_store),
     ("swiftllm_b200.worker.layers.latent_attention", "latent_attention", _latent_attention),
     ("swiftllm_b200.worker.layers.feed_forward", "relu2_inplace", _relu2_inplace),
+    ("swiftllm_b200.worker.buzarax_model", "embed_pair_hash", _embed_pair_hash),
+    ("swiftllm_b200.worker.buzarax_model", "tanh_cap_inplace", _tanh_cap_inplace),
+    ("swiftllm_b200.worker.buzarax_model", "add_rmsnorm_f32", _add_rmsnorm_f32),
+    ("swiftllm_b200.worker.layers.sequential_block", "postnorm_add_mix", _postnorm_add_mix),
+    ("swiftllm_b200.worker.layers.feed_forward", "moe_route_sigmoid", _moe_route_sigmoid),
+    ("swiftllm_b200.worker.layers.feed_forward", "moe_silu_glu_scale", _moe_silu_glu_scale),
+    ("swiftllm_b200.worker.layers.gated_recurrence", "causal_conv", _causal_conv),
+    ("swiftllm_b200.worker.layers.gated_recurrence", "rglru_scan", _rglru_scan),
+    ("swiftllm_b200.worker.layers.linear_attention", "linear_attention", _linear_attention),
+    ("swiftllm_b200.worker.layers.linear_attention", "gated_rmsnorm", _gated_rmsnorm),
     ("swiftllm_b200.worker.layers.feed_forward", "moe_route", _moe_route),
     ("swiftllm_b200.worker.layers.feed_forward", "moe_relu2_scale_inplace", _moe_relu2_scale_inplace),
 ]
