@@ -9,9 +9,10 @@ import numpy as np
 import torch
 
 from oracle import bupozen as O
+from oracle import buzarax as _buzarax
 from oracle import rivudra as _rivudra
 
-_ORACLES = {"Bupozen": O, "Rivudra": _rivudra}
+_ORACLES = {"Bupozen": O, "Rivudra": _rivudra, "Buzarax": _buzarax}
 
 
 def oracle_of(cfg):
