@@ -4,7 +4,7 @@
   python bench.py [--gpus N] [--steps K] [--warmup W]            # this implementation
   python bench.py --impl reference ...                            # CPU arm: torch-eager oracle port on host cores
   torchrun --nproc-per-node N bench.py --gpus N ...               # N > 1: tensor parallel (heads / FFN columns)
-  python bench.py --arch-compare all [--steps K] [--warmup W]     # NOT the headline: Bupozen / Rivudra workers beside the Llama worker
+  python bench.py --arch-compare all [--steps K] [--warmup W]     # NOT the headline: Bupozen / Rivudra / Buzarax workers beside the Llama worker
                                                                   # (prefill / decode tok/s, attention roofline), 1 GPU
 
 Workload (BASELINE.json configs[1]): Llama-3-8B shapes, bf16, pure decode, batch 256, every sequence at
@@ -88,7 +88,7 @@ def parse():
     ap.add_argument("--no-live-traffic", action="store_true", help="skip the ncu DRAM-byte measurement of the decode kernel")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--arch-models", type=str, default="", metavar="NAMES",
-                    help="with --arch-compare: only these workers (comma-separated: bupozen, rivudra, llama); default all")
+                    help="with --arch-compare: only these workers (comma-separated: bupozen, rivudra, buzarax, llama); default all")
     ap.add_argument("--arch-compare", type=str, default="", metavar="SIZES",
                     help="instead of the headline workload: prefill and decode throughput of the Bupozen and Rivudra workers beside the "
                          "Llama worker at equal width / depth (random weights), with the attention kernels' roofline fractions; "
@@ -139,14 +139,25 @@ def _arch_models(sz, dtype, only=None):
                   for _ in range(sz["layers"])]
     riv = {"architecture": "Rivudra", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
            "layers": riv_layers}
-    for name, raw in (("bupozen", bup), ("rivudra", riv), ("llama", llama)):
+    # Buzarax: layers alternate [softmax attention (heads / 4 KV heads, 128 + 128 per head) beside linear attention (128 x 128
+    # state per head)] and [gated linear recurrence of the model's width]; one dense feed-forward, the others 16 / 32 experts
+    attn = {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+            "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    lin = {"heads": H, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5.0 - 3.0 * h / max(1, H - 1)) for h in range(H)]}
+    buz_moe = {"kind": "moe", "expert": {"ff": sz["eff"]}, "router": {"experts": sz["experts"], "top": sz["top"]}}
+    buz_layers = [{"type": "parallel", "mixer": {"left": attn, "right": lin, "left_scale": 0.6, "right_scale": 1.1},
+                   "mlp": {"kind": "dense", "ff": sz["ff"], "limit": 7.0} if i == 0 else buz_moe} if i % 2 == 0 else
+                  {"type": "rglru", "mixer": {"width": W, "blocks": H, "conv": 4}, "mlp": buz_moe} for i in range(sz["layers"])]
+    buz = {"architecture": "Buzarax", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+           "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31}}, "layers": buz_layers}
+    for name, raw in (("bupozen", bup), ("rivudra", riv), ("buzarax", buz), ("llama", llama)):
         if only and name not in only:
             continue
         ec = swiftllm_b200.EngineConfig(model_path="", use_dummy=False, block_size=16, gpu_mem_utilization=0.9, num_cpu_blocks=0,
                                         max_seqs_in_block_table=128, max_blocks_per_seq=512, max_batch_size=64,
                                         max_tokens_in_batch=16384, dtype=dtype)
         model = registry.create_model(ec, registry.model_config_from_dict(raw))
-        model.load_weights(synthetic_getter(seed=0, std=0.02, device="cuda", norm_offset=0.0 if name == "rivudra" else 1.0))
+        model.load_weights(synthetic_getter(seed=0, std=0.02, device="cuda", norm_offset=0.0 if name == "rivudra" else 1.0))   # Buzarax: scalar gains, depth weights and decays come from its loader's own synthetic rules
         model.init_kvcache_and_swap(64 * 4096 // 16 + 64)
         yield name, raw, model
         del model
@@ -196,30 +207,41 @@ def run_arch_compare(args):
         for name, raw, model in _arch_models(sz, "bfloat16", only=[m for m in args.arch_models.split(",") if m]):
             g = torch.Generator().manual_seed(0)
             prompts = [torch.randint(0, sz["vocab"], (prompt_len,), generator=g).tolist() for _ in range(n_prompts)]
+            layers_pkg = "swiftllm_b200.worker.layers."
             if name == "bupozen":
-                mod, attrs = importlib.import_module("swiftllm_b200.worker.layers.latent_attention"), ["latent_attention"]
-            elif name == "rivudra":
-                mod, attrs = importlib.import_module("swiftllm_b200.worker.layers.window_attention"), ["window_attention"]
+                mod, attrs = importlib.import_module(layers_pkg + "latent_attention"), ["latent_attention"]
+            elif name in ("rivudra", "buzarax"):
+                mod, attrs = importlib.import_module(layers_pkg + "window_attention"), ["window_attention"]
             else:
-                mod, attrs = importlib.import_module("swiftllm_b200.worker.layers.transformer_layer"), ["prefill_attention", "paged_attention"]
+                mod, attrs = importlib.import_module(layers_pkg + "transformer_layer"), ["prefill_attention", "paged_attention"]
+            # kernels of the design that the attention column does not cover, timed the same way: label -> (module, attribute)
+            extra = {}
+            if name == "buzarax":
+                extra = {"linear_attention": (importlib.import_module(layers_pkg + "linear_attention"), "linear_attention"),
+                         "rglru_scan": (importlib.import_module(layers_pkg + "gated_recurrence"), "rglru_scan"),
+                         "causal_conv": (importlib.import_module(layers_pkg + "gated_recurrence"), "causal_conv")}
+            extra_ms = {}
 
             def timed(fn, steps, warmup, after=None):
                 total_ms, kern = 0.0, 0.0
                 for it in range(warmup + steps):
                     flush.fill_(it & 0xff)
                     timers = [_KernelTimer(mod, a) for a in attrs]
-                    for t in timers:
+                    more = {k: _KernelTimer(m_, a_) for k, (m_, a_) in extra.items()} if attrs else {}
+                    for t in timers + list(more.values()):
                         t.__enter__()
                     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     e0.record()
                     fn()
                     e1.record()
                     torch.cuda.synchronize()
-                    for t in timers:
+                    for t in timers + list(more.values()):
                         t.__exit__()
                     if it >= warmup:
                         total_ms += e0.elapsed_time(e1)
                         kern += sum(t.ms() for t in timers)
+                        for k, t in more.items():
+                            extra_ms[k] = extra_ms.get(k, 0.0) + t.ms() / steps
                     if after:
                         after()
                 return total_ms / steps, kern / steps
@@ -227,6 +249,7 @@ def run_arch_compare(args):
             sids = list(range(n_prompts))
             pre_ms, pre_attn_ms = timed(lambda: model.forward(prompts, sids, []), args.steps, args.warmup,
                                         after=lambda: model.free_seqs_resources(sids))
+            pre_extra, extra_ms = extra_ms, {}
             # decode state: dec_batch sequences of ctx tokens in the cache (prefilled 4 at a time), then one token each per step
             dids = list(range(dec_batch))
             for i in range(0, dec_batch, 4):
@@ -238,6 +261,7 @@ def run_arch_compare(args):
                     lens[k] += 1
                 model.forward([[1]] * dec_batch, dids, lens)
             dec_ms, dec_attn_ms = timed(dec_step, args.steps, args.warmup)
+            dec_extra, extra_ms = extra_ms, {}
             # the same steps replayed from a CUDA graph (both workers capture pure-decode steps); no per-kernel events in a graph
             model.engine_config.use_cuda_graph = True
             attrs_saved, attrs[:] = list(attrs), []
@@ -263,6 +287,23 @@ def run_arch_compare(args):
                 vis_dec = dec_batch * min(ctx + 1, Wn)
                 fl_dec = L * vis_dec * H * D * 4
                 by_dec = L * vis_dec * 2 * nkv * D * 2
+            elif name == "buzarax":
+                # attention layers: every other one; full causal, q + out + the K / V rows once (prefill), the cache rows (decode)
+                La, Lr, D, nkv, Wd = (L + 1) // 2, L // 2, 128, max(1, H // 4), sz["width"]
+                ntok = n_prompts * prompt_len
+                fl_pre = La * n_prompts * (prompt_len * (prompt_len + 1) // 2) * H * D * 4
+                by_pre = La * ntok * (2 * H + 2 * nkv) * D * 2
+                fl_dec = La * dec_batch * (ctx + 1) * H * D * 4
+                by_dec = La * dec_batch * (ctx + 1) * 2 * nkv * D * 2
+                # label -> (prefill FLOPs, bytes, decode FLOPs, bytes).  linear attention: q, k, v in (2 bytes), fp32 out, 4 dk dv
+                # FLOPs per token and head; decode reads and writes every sequence's fp32 state.  recurrence: u, two gate
+                # logits, the GELU branch in, the product out (2 bytes each); decode adds the fp32 state and the tail, both ways.
+                extra_roof = {
+                    "linear_attention": (La * ntok * H * 4 * D * D, La * ntok * H * (3 * D * 2 + D * 4),
+                                         La * dec_batch * H * 4 * D * D, La * dec_batch * H * (D * D * 8 + 3 * D * 2 + D * 4)),
+                    "rglru_scan": (Lr * ntok * Wd * 30, Lr * ntok * Wd * 10, Lr * dec_batch * Wd * 30, Lr * dec_batch * Wd * (10 + 8 + 12)),
+                    "causal_conv": (Lr * ntok * Wd * 8, Lr * ntok * Wd * 4, Lr * dec_batch * Wd * 8, Lr * dec_batch * Wd * (4 + 6)),
+                }
             else:
                 D, nkv = sz["width"] // H, max(1, H // 4)
                 fl_pre = L * n_prompts * (prompt_len * (prompt_len + 1) // 2) * H * D * 4
@@ -273,7 +314,13 @@ def run_arch_compare(args):
             def roof(fl, by, ms):
                 t_min = max(fl / (peaks["bf16_tflops"] * 1e12), by / (peaks["hbm_gbs"] * 1e9)) * 1e3
                 return round(t_min / ms, 4) if ms > 0 else None
-            emit({"arch_compare": size, "model": name, "dtype": "bf16", "data": "synthetic", "layers": L,
+            other = {}
+            if name == "buzarax":
+                for k, (fp, bp, fd, bd) in extra_roof.items():
+                    other[k] = {"prefill_ms": round(pre_extra.get(k, 0.0), 3), "decode_ms": round(dec_extra.get(k, 0.0), 3),
+                                "prefill_roofline_frac": roof(fp, bp, pre_extra.get(k, 0.0)),
+                                "decode_roofline_frac": roof(fd, bd, dec_extra.get(k, 0.0))}
+            emit({"arch_compare": size, "model": name, "dtype": "bf16", "data": "synthetic", "layers": L, **({"other_kernels": other} if other else {}),
                   "prefill_tokens_per_s": round(n_prompts * prompt_len / pre_ms * 1e3, 1), "prefill_ms": round(pre_ms, 3),
                   "decode_tokens_per_s": round(dec_batch / dec_ms * 1e3, 1), "decode_ms": round(dec_ms, 3),
                   "decode_graph_tokens_per_s": round(dec_batch / graph_ms * 1e3, 1), "decode_graph_ms": round(graph_ms, 3),

@@ -334,14 +334,15 @@ int sllm_moe_silu_glu_scale(const void* u, const void* weights, void* y, int64_t
  * channels], the sequence's last inputs before this step; xin row stride in elements).
  * rglru_scan: gates dtype [blocks, T, 2 * channels / blocks] (logits of the recurrence gate, then of the input gate, per block);
  * a = exp(rate[c] * sigmoid(r)); S <- a S + sqrt(1 - a^2) sigmoid(i) u; out = S * gelu_tanh(ybr); state fp32 [rows, channels];
- * also moves `tail` on by the segment's inputs xin. */
+ * also moves `tail` on by the segment's inputs xin.  The first num_prefill_segs segments (prompt portions) run parallel over time
+ * (tiles of 64 tokens whose eight runs are composed as maps S -> a S + b), the rest one thread per channel. */
 int sllm_causal_conv(const void* xin, int64_t xin_stride, const void* w, const void* bias, const void* tail, const void* tok_seq,
-                     const void* tok_pos, void* u, int64_t num_tokens, int channels, int taps, sllm_dtype_t dtype,
-                     sllm_stream_t stream);
+                     const void* tok_pos, void* u, int64_t num_tokens, int64_t num_prefill_tokens, int channels, int taps,
+                     sllm_dtype_t dtype, sllm_stream_t stream);
 int sllm_rglru_scan(const void* u, const void* gates, int blocks, const void* ybr, int64_t y_stride, const void* rate,
                     const void* xin, int64_t xin_stride, void* state, void* tail, const void* seg_starts, const void* seq_ids,
-                    const void* tok_pos, void* out, int64_t num_tokens, int num_segs, int channels, int taps, sllm_dtype_t dtype,
-                    sllm_stream_t stream);
+                    const void* tok_pos, void* out, int64_t num_tokens, int num_segs, int num_prefill_segs, int channels, int taps,
+                    sllm_dtype_t dtype, sllm_stream_t stream);
 /* linear_attention: per head S <- decay[h] S + silu(k) silu(v)^T, out[t, h] (fp32 [T, heads * dv]) = S^T silu(q); q, k
  * [T, heads * dk], v [T, heads * dv] pre-activation (row strides in elements); state fp32 [rows, heads, dk, dv].
  * gated_rmsnorm: out = x / sqrt(mean(x^2) + eps) * weight * sigmoid(gate) * out_scale; x fp32 [T, n], weight fp32 [n], gate

@@ -65,8 +65,8 @@ SIGNATURES = {
     "sllm_tanh_cap_inplace": (_I, [_P, _L, _F, _I, _P]),
     "sllm_moe_route_sigmoid": (_I, [_P, _P, _P, _L, _I, _I, _P]),
     "sllm_moe_silu_glu_scale": (_I, [_P, _P, _P, _L, _I, _I, _I, _P]),
-    "sllm_causal_conv": (_I, [_P, _L, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _P]),
-    "sllm_rglru_scan": (_I, [_P, _P, _I, _P, _L, _P, _P, _L, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _P]),
+    "sllm_causal_conv": (_I, [_P, _L, _P, _P, _P, _P, _P, _P, _L, _L, _I, _I, _I, _P]),
+    "sllm_rglru_scan": (_I, [_P, _P, _I, _P, _L, _P, _P, _L, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _P]),
     "sllm_linear_attention": (_I, [_P, _L, _P, _L, _P, _L, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "sllm_gated_rmsnorm": (_I, [_P, _P, _P, _L, _F, _F, _P, _L, _L, _I, _I, _P]),
 }

@@ -16,32 +16,55 @@ namespace sllm {
 
 constexpr int CONV_MAX_TAPS = 8;
 
-// grid (T, ceil(C / 256)).  tail: [rows, K-1, C] (slot i: the input K-1-i positions before the next one).
-template <typename T>
-__global__ void __launch_bounds__(256) causal_conv_kernel(const T* __restrict__ xin, int64_t xin_stride, const T* __restrict__ w,
+// grid (ceil(T / CONV_TOKENS), ceil(C / 128)).  tail: [rows, K-1, C] (slot i: the input K-1-i positions before the next one).
+// A thread walks CONV_TOKENS consecutive rows of one channel and keeps the last K-1 inputs in registers; where a row does not
+// continue the row above (another sequence, or the first row of the tile) the window is filled again: from the rows above as far
+// as they are the sequence's previous positions, from the sequence's tail before that, zeros before position 0.
+// Rows [row0, row_end) of the batch; CONV_TOKENS = 16 for prompt portions, 1 for single decoded tokens (whose window is filled
+// from the tail for every row, all rows at once).
+template <typename T, int CONV_TOKENS>
+__global__ void __launch_bounds__(128) causal_conv_kernel(const T* __restrict__ xin, int64_t xin_stride, const T* __restrict__ w,
                                                           const T* __restrict__ bias, const T* __restrict__ tail,
                                                           const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
-                                                          T* __restrict__ u, int C, int K) {
-    const int64_t t = blockIdx.x;
+                                                          T* __restrict__ u, int64_t row0, int64_t row_end, int C, int K) {
+    const int64_t tile0 = row0 + (int64_t)blockIdx.x * CONV_TOKENS;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= C) return;
-    const int seq = tok_seq[t], pos = tok_pos[t];
-    // rows above this one that are the sequence's previous positions
-    int above = 0;
-    while (above < K - 1 && t - above - 1 >= 0 && tok_seq[t - above - 1] == seq && tok_pos[t - above - 1] == pos - above - 1) above++;
-    float acc = bias != nullptr ? ldf(bias + c) : 0.f;
-    for (int k = 0; k < K; k++) {
-        if (pos - k < 0) break;
-        float v;
-        if (k <= above) {
-            v = ldf(xin + (t - k) * xin_stride + c);
-        } else {
-            // position pos - k lies before the segment, which starts at pos - above: tail slot K-1 - (k - above)
-            v = ldf(tail + ((int64_t)seq * (K - 1) + (K - 1 - (k - above))) * C + c);
+    float wk[CONV_MAX_TAPS], hist[CONV_MAX_TAPS];       // wk[k]: weight of the input k positions back; hist[k - 1]: that input
+#pragma unroll
+    for (int k = 0; k < CONV_MAX_TAPS; k++) { wk[k] = k < K ? ldf(w + (int64_t)c * K + (K - 1 - k)) : 0.f; hist[k] = 0.f; }
+    const float b0 = bias != nullptr ? ldf(bias + c) : 0.f;
+    const int nrows = (int)min((int64_t)CONV_TOKENS, row_end - tile0);
+    float xv[CONV_TOKENS];
+#pragma unroll
+    for (int i = 0; i < CONV_TOKENS; i++) xv[i] = i < nrows ? ldf(xin + (tile0 + i) * xin_stride + c) : 0.f;
+    int prev_seq = -1, prev_pos = -2;
+#pragma unroll
+    for (int i = 0; i < CONV_TOKENS; i++) {
+        if (i >= nrows) break;
+        const int64_t t = tile0 + i;
+        const int seq = tok_seq[t], pos = tok_pos[t];
+        if (i == 0 || seq != prev_seq || pos != prev_pos + 1) {
+            int above = 0;                              // rows above this one that are the sequence's previous positions
+            while (above < K - 1 && t - above - 1 >= 0 && tok_seq[t - above - 1] == seq && tok_pos[t - above - 1] == pos - above - 1) above++;
+#pragma unroll
+            for (int k = 1; k < CONV_MAX_TAPS; k++) {
+                float v = 0.f;
+                if (k < K && pos - k >= 0)
+                    v = k <= above ? ldf(xin + (t - k) * xin_stride + c)
+                                   : ldf(tail + ((int64_t)seq * (K - 1) + (K - 1 - (k - above))) * C + c);
+                hist[k - 1] = v;
+            }
         }
-        acc += ldf(w + (int64_t)c * K + (K - 1 - k)) * v;
+        float acc = b0 + wk[0] * xv[i];
+#pragma unroll
+        for (int k = 1; k < CONV_MAX_TAPS; k++) acc += wk[k] * hist[k - 1];
+        stf(u + t * C + c, acc);
+#pragma unroll
+        for (int k = CONV_MAX_TAPS - 1; k >= 1; k--) hist[k] = hist[k - 1];
+        hist[0] = xv[i];
+        prev_seq = seq; prev_pos = pos;
     }
-    stf(u + t * C + c, acc);
 }
 
 __device__ __forceinline__ float gelu_tanh_f(float z) {
@@ -72,7 +95,7 @@ __global__ void __launch_bounds__(128) rglru_scan_kernel(
         const float r = sigmoid_f(ldf(gr + (int64_t)i * 2 * cb)), g = sigmoid_f(ldf(gr + (int64_t)i * 2 * cb + cb));
         const float log_a = rt * r;
         const float a = expf(log_a);
-        S = a * S + sqrtf(fmaxf(1.f - expf(2.f * log_a), 0.f)) * (g * x);
+        S = a * S + sqrtf(-expm1f(2.f * log_a)) * (g * x);              // 1 - a^2 without cancellation near a = 1
         stf(out + t * C + c, S * gelu_tanh_f(ldf(ybr + t * y_stride + c)));
     }
     state[(int64_t)seq * C + c] = S;
@@ -89,67 +112,237 @@ __global__ void __launch_bounds__(128) rglru_scan_kernel(
     }
 }
 
-// grid (segments, heads), 256 threads.  Thread (sl, j): column j of the state, rows sl, sl + nsl, ... (at most R of them).
+// The same recurrence for PROMPT PORTIONS, parallel over time as well: grid (segments, ceil(C / 32)), 8 warps.  Lane: channel;
+// warp w: tokens w TT .. w TT + TT - 1 of the current tile of 8 TT tokens.  Every thread turns its tokens' gates into the pairs
+// (a, b) of S <- a S + b (the sigmoids, exponentials, root and the GELU branch are the expensive part and run for 8 TT tokens at
+// once), folds them into one pair for its run, the eight pairs of a tile meet in shared memory, every thread composes the state
+// at its run's start (and the state after the tile) from them and replays its run.  Composition of the maps S -> a S + b is exact
+// algebra; in floating point the result differs from the token-by-token loop by rounding only.
+constexpr int SCAN_WARPS = 8;
+
+template <typename T, int TT>
+__global__ void __launch_bounds__(SCAN_WARPS * 32) rglru_scan_tiled_kernel(
+    const T* __restrict__ u, const T* __restrict__ gates, int cb, const T* __restrict__ ybr, int64_t y_stride,
+    const float* __restrict__ rate, const T* __restrict__ xin, int64_t xin_stride, float* __restrict__ state,
+    T* __restrict__ tail, const int* __restrict__ seg_starts, const int* __restrict__ seq_ids, const int* __restrict__ tok_pos,
+    T* __restrict__ out, int64_t num_tokens, int C, int K) {
+    __shared__ float sA[SCAN_WARPS][32], sB[SCAN_WARPS][32];
+    const int b = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = blockIdx.y * 32 + lane;
+    const int t0 = seg_starts[b], n = seg_starts[b + 1] - t0;
+    if (n <= 0) return;
+    const bool ok = c < C;
+    const int cs = ok ? c : 0;                          // dead lanes walk channel 0 and store nothing
+    const int seq = seq_ids[b], p0 = tok_pos[t0];
+    const int blk = cs / cb, cc = cs - blk * cb;
+    const float rt = rate[cs];
+    float carry = p0 > 0 ? state[(int64_t)seq * C + cs] : 0.f;
+    const T* gr = gates + ((int64_t)blk * num_tokens + t0) * 2 * cb + cc;
+    for (int tile0 = 0; tile0 < n; tile0 += SCAN_WARPS * TT) {
+        const int i0 = tile0 + warp * TT;
+        float a[TT], bb[TT], gy[TT];
+        float A = 1.f, B = 0.f;
+        // every load of the run is issued before the first result is needed (rows past the segment's end re-read its last row)
+#pragma unroll
+        for (int j = 0; j < TT; j++) {
+            const int64_t i = min(i0 + j, n - 1), t = t0 + i;
+            a[j] = ldf(gr + i * 2 * cb);
+            bb[j] = ldf(gr + i * 2 * cb + cb);
+            gy[j] = ldf(ybr + t * y_stride + cs);
+        }
+        float xr[TT];
+#pragma unroll
+        for (int j = 0; j < TT; j++) xr[j] = ldf(u + (int64_t)(t0 + min(i0 + j, n - 1)) * C + cs);
+#pragma unroll
+        for (int j = 0; j < TT; j++) {
+            if (i0 + j < n) {
+                const float r = sigmoid_f(a[j]), g = sigmoid_f(bb[j]);
+                const float log_a = rt * r;
+                a[j] = expf(log_a);
+                bb[j] = sqrtf(-expm1f(2.f * log_a)) * (g * xr[j]);              // 1 - a^2 without cancellation near a = 1
+                gy[j] = gelu_tanh_f(gy[j]);
+                B = a[j] * B + bb[j];
+                A *= a[j];
+            } else {
+                a[j] = 1.f; bb[j] = 0.f; gy[j] = 0.f;
+            }
+        }
+        sA[warp][lane] = A;
+        sB[warp][lane] = B;
+        __syncthreads();
+        float S = carry;
+        for (int w = 0; w < warp; w++) S = sA[w][lane] * S + sB[w][lane];
+        float E = S;                                    // every warp composes the state after the tile in the same order
+        for (int w = warp; w < SCAN_WARPS; w++) E = sA[w][lane] * E + sB[w][lane];
+        carry = E;
+#pragma unroll
+        for (int j = 0; j < TT; j++) {
+            if (i0 + j < n) {
+                S = a[j] * S + bb[j];
+                if (ok) stf(out + (int64_t)(t0 + i0 + j) * C + c, S * gy[j]);
+            }
+        }
+        __syncthreads();                                // sA / sB are rewritten by the next tile
+    }
+    if (warp != 0 || !ok) return;
+    state[(int64_t)seq * C + c] = carry;
+    float old[CONV_MAX_TAPS];
+    T* tl = tail + (int64_t)seq * (K - 1) * C + c;
+    for (int i = 0; i < K - 1; i++) old[i] = p0 > 0 ? ldf(tl + (int64_t)i * C) : 0.f;
+    for (int i = 0; i < K - 1; i++) {
+        const int rel = n - (K - 1) + i;
+        float v = 0.f;
+        if (rel >= 0) v = ldf(xin + (int64_t)(t0 + rel) * xin_stride + c);
+        else if (p0 + rel >= 0 && rel + K - 1 >= 0) v = old[rel + K - 1];
+        stf(tl + (int64_t)i * C, v);
+    }
+}
+
+// silu of a projection's output.  With 16-bit storage the activation only has to be good to that type's rounding: fast exponential
+// and division; with fp32 storage the accurate ones.
+template <typename T>
+__device__ __forceinline__ float silu_act(float z) {
+    if constexpr (sizeof(T) == 4) return z * sigmoid_f(z);
+    else return __fdividef(z, 1.f + __expf(-z));
+}
+
+// Linear attention with a constant decay per head.  The columns of a head's state S [dk, dv] never mix (out[j] = sum_d S[d, j] q[d],
+// S[d, j] <- decay S[d, j] + k[d] v[j]), so a CTA owns LA_COLS columns of one (segment, head): grid (segments, heads,
+// ceil(dv / LA_COLS)), 8 warps.  Lane j: column; warp w: rows w R .. w R + R - 1 of the state, in registers for the whole segment.
+// Tokens are staged LA_TOKENS at a time (silu applied once, rows padded with zeros to 8 R); every warp walks them without a
+// barrier and keeps its partial dot products in registers; the eight partial sums per (token, column) meet in shared memory once
+// per batch.
+// Inside a batch the decay is folded into the staged vectors: with U_i = S_start + sum_{j <= i} decay^-(j+1) k_j v_j^T the state
+// after token i is decay^(i+1) U_i, so k_j is staged times decay^-(j+1), q_i times decay^(i+1), the update is ONE fused
+// multiply-add per state entry (plus one for the dot product), and the state is scaled by decay^tokens once per batch.  Eight
+// tokens keep the factors within 2^32 for decay >= 1/16; a smaller decay takes the direct form (decay * S + k v).
+constexpr int LA_COLS = 32;
+constexpr float LA_MIN_FOLDED_DECAY = 0.0625f;
+constexpr int LA_TOKENS = 8;
+constexpr int LA_WARPS = 8;
+
 template <typename T, int R>
-__global__ void __launch_bounds__(256) linear_attention_kernel(
+__global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_kernel(
     const T* __restrict__ q, int64_t q_stride, const T* __restrict__ k, int64_t k_stride, const T* __restrict__ v, int64_t v_stride,
     const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ seg_starts, const int* __restrict__ seq_ids,
-    const int* __restrict__ tok_pos, float* __restrict__ out, int H, int dk, int dv, int nsl) {
-    extern __shared__ float sm[];
-    float* qs = sm;                 // [dk]
-    float* ks = qs + dk;            // [dk]
-    float* vs = ks + dk;            // [dv]
-    float* red = vs + dv;           // [nsl][dv]
+    const int* __restrict__ tok_pos, float* __restrict__ out, int H, int dk, int dv) {
+    constexpr int DKP = LA_WARPS * R;                                   // padded rows
+    __shared__ __align__(16) float qs[LA_TOKENS][DKP];
+    __shared__ __align__(16) float ks[LA_TOKENS][DKP];
+    __shared__ float vs[LA_TOKENS][LA_COLS];
+    __shared__ float red[LA_WARPS][LA_TOKENS][LA_COLS];
+    __shared__ float fq[LA_TOKENS], fk[LA_TOKENS];                      // decay^(i+1) and its inverse (1 in the direct form)
     const int b = blockIdx.x, h = blockIdx.y;
     const int t0 = seg_starts[b], n = seg_starts[b + 1] - t0;
     if (n <= 0) return;
     const int seq = seq_ids[b], p0 = tok_pos[t0];
-    const int tid = threadIdx.x;
-    const bool active = tid < nsl * dv;
-    const int j = tid % dv, sl = tid / dv;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int col = blockIdx.z * LA_COLS + lane;
+    const bool col_ok = col < dv;
     const float lam = decay[h];
+    const bool folded = lam >= LA_MIN_FOLDED_DECAY;
+    if (tid < LA_TOKENS) {
+        const float pw = folded ? powf(lam, (float)(tid + 1)) : 1.f;
+        fq[tid] = pw;
+        fk[tid] = 1.f / pw;
+    }
     float* st = state + ((int64_t)seq * H + h) * dk * dv;
     float S[R];
 #pragma unroll
     for (int r = 0; r < R; r++) {
-        const int d = sl + r * nsl;
-        S[r] = (active && d < dk && p0 > 0) ? st[(int64_t)d * dv + j] : 0.f;
+        const int d = warp * R + r;
+        S[r] = (col_ok && d < dk && p0 > 0) ? st[(int64_t)d * dv + col] : 0.f;
     }
-    for (int i = 0; i < n; i++) {
-        const int64_t t = t0 + i;
-        __syncthreads();                    // the previous token's vectors and partial sums are done with
-        for (int d = tid; d < dk; d += blockDim.x) {
-            const float a = ldf(q + t * q_stride + (int64_t)h * dk + d), c = ldf(k + t * k_stride + (int64_t)h * dk + d);
-            qs[d] = a * sigmoid_f(a);
-            ks[d] = c * sigmoid_f(c);
-        }
-        for (int d = tid; d < dv; d += blockDim.x) { const float a = ldf(v + t * v_stride + (int64_t)h * dv + d); vs[d] = a * sigmoid_f(a); }
-        __syncthreads();
-        if (active) {
-            const float vj = vs[j];
-            float part = 0.f;
+    __syncthreads();                                                    // fq / fk
+    // raw inputs of one batch, as this thread stages them: NQ entries of q and of k (entry idx = tid + e * 256 of the padded
+    // [LA_TOKENS][DKP] tile), one of v (warp i stages token i's columns)
+    constexpr int NQ = LA_TOKENS * DKP / (LA_WARPS * 32);
+    float rq[NQ], rk[NQ], rv;
+    auto fetch = [&](int i0) {
+        const int nt = min(LA_TOKENS, n - i0);
 #pragma unroll
-            for (int r = 0; r < R; r++) {
-                const int d = sl + r * nsl;
-                if (d < dk) {
-                    S[r] = lam * S[r] + ks[d] * vj;
-                    part += S[r] * qs[d];
-                }
+        for (int e = 0; e < NQ; e++) {
+            const int idx = tid + e * (LA_WARPS * 32);
+            const int i = idx / DKP, d = idx - i * DKP;
+            rq[e] = 0.f; rk[e] = 0.f;
+            if (i < nt && d < dk) {
+                const int64_t t = t0 + i0 + i;
+                rq[e] = ldf(q + t * q_stride + (int64_t)h * dk + d);
+                rk[e] = ldf(k + t * k_stride + (int64_t)h * dk + d);
             }
-            red[sl * dv + j] = part;
         }
+        rv = (warp < nt && col_ok) ? ldf(v + (int64_t)(t0 + i0 + warp) * v_stride + (int64_t)h * dv + col) : 0.f;
+    };
+    fetch(0);
+    for (int i0 = 0; i0 < n; i0 += LA_TOKENS) {
+        const int nt = min(LA_TOKENS, n - i0);
+        // stage the batch: silu(q), silu(k) (zeros from dk on), silu(v) of this CTA's columns (silu(0) = 0 keeps the padding)
+#pragma unroll
+        for (int e = 0; e < NQ; e++) {
+            const int idx = tid + e * (LA_WARPS * 32);
+            const int i = idx / DKP, d = idx - i * DKP;
+            qs[i][d] = silu_act<T>(rq[e]) * fq[i];
+            ks[i][d] = silu_act<T>(rk[e]) * fk[i];
+        }
+        vs[warp][lane] = silu_act<T>(rv);
+        if (i0 + LA_TOKENS < n) fetch(i0 + LA_TOKENS);        // in flight while this batch is multiplied
         __syncthreads();
-        if (tid < dv) {
-            float o = 0.f;
-            for (int s = 0; s < nsl; s++) o += red[s * dv + tid];
-            out[t * ((int64_t)H * dv) + (int64_t)h * dv + tid] = o;
+        float part[LA_TOKENS];
+#pragma unroll
+        for (int i = 0; i < LA_TOKENS; i++) {
+            part[i] = 0.f;
+            if (i < nt) {                                               // uniform over the CTA
+                const float vj = vs[i][lane];
+                float acc = 0.f;
+                if (folded) {                                           // uniform over the CTA
+#pragma unroll
+                    for (int r = 0; r < R; r += 4) {
+                        const float4 k4 = *reinterpret_cast<const float4*>(&ks[i][warp * R + r]);
+                        const float4 q4 = *reinterpret_cast<const float4*>(&qs[i][warp * R + r]);
+                        S[r] = fmaf(k4.x, vj, S[r]);         acc = fmaf(S[r], q4.x, acc);
+                        S[r + 1] = fmaf(k4.y, vj, S[r + 1]); acc = fmaf(S[r + 1], q4.y, acc);
+                        S[r + 2] = fmaf(k4.z, vj, S[r + 2]); acc = fmaf(S[r + 2], q4.z, acc);
+                        S[r + 3] = fmaf(k4.w, vj, S[r + 3]); acc = fmaf(S[r + 3], q4.w, acc);
+                    }
+                } else {
+#pragma unroll
+                    for (int r = 0; r < R; r += 4) {
+                        const float4 k4 = *reinterpret_cast<const float4*>(&ks[i][warp * R + r]);
+                        const float4 q4 = *reinterpret_cast<const float4*>(&qs[i][warp * R + r]);
+                        S[r] = lam * S[r] + k4.x * vj;         acc += S[r] * q4.x;
+                        S[r + 1] = lam * S[r + 1] + k4.y * vj; acc += S[r + 1] * q4.y;
+                        S[r + 2] = lam * S[r + 2] + k4.z * vj; acc += S[r + 2] * q4.z;
+                        S[r + 3] = lam * S[r + 3] + k4.w * vj; acc += S[r + 3] * q4.w;
+                    }
+                }
+                part[i] = acc;
+            }
         }
+        if (folded) {
+            const float back = fq[nt - 1];                              // U -> S = decay^tokens U
+#pragma unroll
+            for (int r = 0; r < R; r++) S[r] *= back;
+        }
+#pragma unroll
+        for (int i = 0; i < LA_TOKENS; i++) red[warp][i][lane] = part[i];
+        __syncthreads();                    // partial sums visible; qs / ks / vs are done with and may be staged again
+        {
+            const int i = warp;                                         // warp i adds up token i
+            if (i < nt && col_ok) {
+                float o = 0.f;
+#pragma unroll
+                for (int w = 0; w < LA_WARPS; w++) o += red[w][i][lane];
+                out[(int64_t)(t0 + i0 + i) * ((int64_t)H * dv) + (int64_t)h * dv + col] = o;
+            }
+        }
+        // the next batch writes `red` only after its own first barrier, which every warp reaches after this read
     }
-    if (active) {
+    if (col_ok) {
 #pragma unroll
         for (int r = 0; r < R; r++) {
-            const int d = sl + r * nsl;
-            if (d < dk) st[(int64_t)d * dv + j] = S[r];
+            const int d = warp * R + r;
+            if (d < dk) st[(int64_t)d * dv + col] = S[r];
         }
     }
 }
@@ -176,21 +369,17 @@ template <typename T>
 static int launch_linear_attention(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v, int64_t v_stride,
                                    const void* decay, void* state, const void* seg_starts, const void* seq_ids, const void* tok_pos,
                                    void* out, int num_segs, int H, int dk, int dv, cudaStream_t stream) {
-    int nsl = 256 / dv;
-    if (nsl > dk) nsl = dk;
-    const int rows = (dk + nsl - 1) / nsl;
-    const size_t smem = (size_t)(2 * dk + dv + nsl * dv) * sizeof(float);
-    const dim3 grid((unsigned)num_segs, (unsigned)H);
+    const int rows = cdiv(dk, LA_WARPS);                                // state rows per warp
+    const dim3 grid((unsigned)num_segs, (unsigned)H, (unsigned)cdiv(dv, LA_COLS));
 #define LA(R)                                                                                                                  \
-    linear_attention_kernel<T, R><<<grid, 256, smem, stream>>>((const T*)q, q_stride, (const T*)k, k_stride, (const T*)v, v_stride, \
-        (const float*)decay, (float*)state, (const int*)seg_starts, (const int*)seq_ids, (const int*)tok_pos, (float*)out, H, dk,  \
-        dv, nsl)
-    if (rows <= 4) LA(4);
+    linear_attention_kernel<T, R><<<grid, LA_WARPS * 32, 0, stream>>>((const T*)q, q_stride, (const T*)k, k_stride, (const T*)v,  \
+        v_stride, (const float*)decay, (float*)state, (const int*)seg_starts, (const int*)seq_ids, (const int*)tok_pos,         \
+        (float*)out, H, dk, dv)
+    if (rows <= 4) LA(4);                                               // R is a multiple of 4: whole float4 reads, R / 4 staged entries per thread
     else if (rows <= 8) LA(8);
     else if (rows <= 16) LA(16);
     else if (rows <= 32) LA(32);
-    else if (rows <= 64) LA(64);
-    else LA(128);
+    else LA(64);
 #undef LA
     return check_launch("linear_attention");
 }
@@ -202,46 +391,64 @@ using namespace sllm;
 extern "C" {
 
 int sllm_causal_conv(const void* xin, int64_t xin_stride, const void* w, const void* bias, const void* tail, const void* tok_seq,
-                     const void* tok_pos, void* u, int64_t num_tokens, int channels, int taps, sllm_dtype_t dtype,
-                     sllm_stream_t stream) {
+                     const void* tok_pos, void* u, int64_t num_tokens, int64_t num_prefill_tokens, int channels, int taps,
+                     sllm_dtype_t dtype, sllm_stream_t stream) {
     SLLM_REQUIRE(num_tokens >= 0 && channels > 0 && taps >= 1 && taps <= CONV_MAX_TAPS, "causal_conv: 1 <= taps <= %d (got %d)",
                  CONV_MAX_TAPS, taps);
+    SLLM_REQUIRE(num_prefill_tokens >= 0 && num_prefill_tokens <= num_tokens, "causal_conv: bad number of prompt rows");
     if (num_tokens == 0) return 0;
     SLLM_REQUIRE(xin && w && tok_seq && tok_pos && u && (taps == 1 || tail), "causal_conv: null pointer");
-    const dim3 grid((unsigned)num_tokens, (unsigned)cdiv(channels, 256));
-    SLLM_DISPATCH_DTYPE_F32(dtype, (causal_conv_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
-        (const T*)xin, xin_stride, (const T*)w, (const T*)bias, (const T*)tail, (const int*)tok_seq, (const int*)tok_pos, (T*)u,
-        channels, taps)));
+    if (num_prefill_tokens > 0) {
+        const dim3 grid((unsigned)cdiv(num_prefill_tokens, 16), (unsigned)cdiv(channels, 128));
+        SLLM_DISPATCH_DTYPE_F32(dtype, (causal_conv_kernel<T, 16><<<grid, 128, 0, (cudaStream_t)stream>>>(
+            (const T*)xin, xin_stride, (const T*)w, (const T*)bias, (const T*)tail, (const int*)tok_seq, (const int*)tok_pos, (T*)u,
+            (int64_t)0, num_prefill_tokens, channels, taps)));
+        if (check_launch("causal_conv (prompt portions)")) return 1;
+    }
+    if (num_tokens > num_prefill_tokens) {
+        const dim3 grid((unsigned)(num_tokens - num_prefill_tokens), (unsigned)cdiv(channels, 128));
+        SLLM_DISPATCH_DTYPE_F32(dtype, (causal_conv_kernel<T, 1><<<grid, 128, 0, (cudaStream_t)stream>>>(
+            (const T*)xin, xin_stride, (const T*)w, (const T*)bias, (const T*)tail, (const int*)tok_seq, (const int*)tok_pos, (T*)u,
+            num_prefill_tokens, num_tokens, channels, taps)));
+    }
     return check_launch("causal_conv");
 }
 
 int sllm_rglru_scan(const void* u, const void* gates, int blocks, const void* ybr, int64_t y_stride, const void* rate,
                     const void* xin, int64_t xin_stride, void* state, void* tail, const void* seg_starts, const void* seq_ids,
-                    const void* tok_pos, void* out, int64_t num_tokens, int num_segs, int channels, int taps, sllm_dtype_t dtype,
-                    sllm_stream_t stream) {
+                    const void* tok_pos, void* out, int64_t num_tokens, int num_segs, int num_prefill_segs, int channels, int taps,
+                    sllm_dtype_t dtype, sllm_stream_t stream) {
     SLLM_REQUIRE(num_tokens >= 0 && num_segs >= 0 && channels > 0 && blocks > 0 && channels % blocks == 0 && taps >= 1 &&
                  taps <= CONV_MAX_TAPS, "rglru_scan: bad shape (channels %d in %d blocks, %d taps)", channels, blocks, taps);
+    SLLM_REQUIRE(num_prefill_segs >= 0 && num_prefill_segs <= num_segs, "rglru_scan: %d prompt segments of %d", num_prefill_segs,
+                 num_segs);
     if (num_tokens == 0 || num_segs == 0) return 0;
     SLLM_REQUIRE(u && gates && ybr && rate && xin && state && (taps == 1 || tail) && seg_starts && seq_ids && tok_pos && out,
                  "rglru_scan: null pointer");
-    const dim3 grid((unsigned)num_segs, (unsigned)cdiv(channels, 128));
-    SLLM_DISPATCH_DTYPE_F32(dtype, (rglru_scan_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>(
-        (const T*)u, (const T*)gates, channels / blocks, (const T*)ybr, y_stride, (const float*)rate, (const T*)xin, xin_stride,
-        (float*)state, (T*)tail, (const int*)seg_starts, (const int*)seq_ids, (const int*)tok_pos, (T*)out, num_tokens, channels,
-        taps)));
+    // prompt portions (the first segments): parallel over time; single decoded tokens: one thread per channel
+    if (num_prefill_segs > 0) {
+        const dim3 grid((unsigned)num_prefill_segs, (unsigned)cdiv(channels, 32));
+        SLLM_DISPATCH_DTYPE_F32(dtype, (rglru_scan_tiled_kernel<T, 8><<<grid, SCAN_WARPS * 32, 0, (cudaStream_t)stream>>>(
+            (const T*)u, (const T*)gates, channels / blocks, (const T*)ybr, y_stride, (const float*)rate, (const T*)xin, xin_stride,
+            (float*)state, (T*)tail, (const int*)seg_starts, (const int*)seq_ids, (const int*)tok_pos, (T*)out, num_tokens,
+            channels, taps)));
+        if (check_launch("rglru_scan (prompt portions)")) return 1;
+    }
+    if (num_segs > num_prefill_segs) {
+        const dim3 grid((unsigned)(num_segs - num_prefill_segs), (unsigned)cdiv(channels, 128));
+        SLLM_DISPATCH_DTYPE_F32(dtype, (rglru_scan_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>(
+            (const T*)u, (const T*)gates, channels / blocks, (const T*)ybr, y_stride, (const float*)rate, (const T*)xin, xin_stride,
+            (float*)state, (T*)tail, (const int*)seg_starts + num_prefill_segs, (const int*)seq_ids + num_prefill_segs,
+            (const int*)tok_pos, (T*)out, num_tokens, channels, taps)));
+    }
     return check_launch("rglru_scan");
 }
 
 int sllm_linear_attention(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v, int64_t v_stride,
                           const void* decay, void* state, const void* seg_starts, const void* seq_ids, const void* tok_pos,
                           void* out, int num_segs, int num_heads, int dk, int dv, sllm_dtype_t dtype, sllm_stream_t stream) {
-    SLLM_REQUIRE(num_segs >= 0 && num_heads > 0 && dk > 0 && dv > 0 && dv <= 256, "linear_attention: bad shape (dk %d, dv %d <= 256)",
-                 dk, dv);
-    {
-        int nsl = 256 / dv;
-        if (nsl > dk) nsl = dk;
-        SLLM_REQUIRE((dk + nsl - 1) / nsl <= 128, "linear_attention: a %d x %d state does not fit one CTA's registers", dk, dv);
-    }
+    SLLM_REQUIRE(num_segs >= 0 && num_heads > 0 && dk > 0 && dv > 0 && dk <= 64 * LA_WARPS && cdiv(dv, LA_COLS) <= 65535,
+                 "linear_attention: bad shape (dk %d <= %d, dv %d)", dk, 64 * LA_WARPS, dv);
     if (num_segs == 0) return 0;
     SLLM_REQUIRE(q && k && v && decay && state && seg_starts && seq_ids && tok_pos && out, "linear_attention: null pointer");
     SLLM_DISPATCH_DTYPE_F32(dtype, return (launch_linear_attention<T>(q, q_stride, k, k_stride, v, v_stride, decay, state, seg_starts,

@@ -20,7 +20,7 @@ def causal_conv(xin: torch.Tensor, w: torch.Tensor, bias, tail: torch.Tensor, in
     u = torch.empty((T, C), dtype=xin.dtype, device=xin.device)
     _lib.check(_lib.lib().sllm_causal_conv(xin.data_ptr(), _stride0(xin), w.data_ptr(), _lib.ptr(bias), _lib.ptr(tail),
                                            infer_state.token_seq_ids.data_ptr(), infer_state.token_positions.data_ptr(), u.data_ptr(),
-                                           T, C, taps, _lib.dtype_tag_f32(xin.dtype), _lib.stream()), "causal_conv")
+                                           T, min(T, max(0, int(getattr(infer_state, "num_prefill_tokens", T)))), C, taps, _lib.dtype_tag_f32(xin.dtype), _lib.stream()), "causal_conv")
     return u
 
 
@@ -28,7 +28,8 @@ def rglru_scan(u: torch.Tensor, gates: torch.Tensor, ybr: torch.Tensor, rate: to
                tail: torch.Tensor, infer_state) -> torch.Tensor:
     """u [T, C]; gates [blocks, T, 2 * C / blocks] logits (recurrence gate | input gate); ybr [T, C] pre-activation of the GELU
     branch; rate fp32 [C] (log a = rate * sigmoid(r)); xin [T, C] the convolution's inputs (for the tail); state fp32 [rows, C].
-    -> S * gelu(ybr) [T, C]; state and tail move on."""
+    -> S * gelu(ybr) [T, C]; state and tail move on.  The first infer_state.num_prefill_seqs segments (prompt portions) go
+    through the kernel that is parallel over time, the rest (single decoded tokens) through the one-thread-per-channel kernel."""
     T, C = u.shape
     blocks, taps = gates.shape[0], tail.shape[1] + 1
     assert u.is_contiguous() and gates.is_contiguous() and gates.shape == (blocks, T, 2 * C // blocks) and gates.dtype == u.dtype
@@ -39,8 +40,8 @@ def rglru_scan(u: torch.Tensor, gates: torch.Tensor, ybr: torch.Tensor, rate: to
     out = torch.empty((T, C), dtype=u.dtype, device=u.device)
     _lib.check(_lib.lib().sllm_rglru_scan(u.data_ptr(), gates.data_ptr(), blocks, ybr.data_ptr(), _stride0(ybr), rate.data_ptr(),
                                           xin.data_ptr(), _stride0(xin), state.data_ptr(), tail.data_ptr(), st.seg_starts.data_ptr(),
-                                          st.seq_ids.data_ptr(), st.token_positions.data_ptr(), out.data_ptr(), T, st.batch_size, C,
-                                          taps, _lib.dtype_tag_f32(u.dtype), _lib.stream()), "rglru_scan")
+                                          st.seq_ids.data_ptr(), st.token_positions.data_ptr(), out.data_ptr(), T, st.batch_size,
+                                          min(st.batch_size, max(0, int(getattr(st, "num_prefill_seqs", st.batch_size)))), C, taps, _lib.dtype_tag_f32(u.dtype), _lib.stream()), "rglru_scan")
     return out
 
 

@@ -131,3 +131,11 @@ def test_score_cap_binds(cpu):
 
 def test_first_tokens_and_block_borders(cpu):
     C.case_first_tokens_and_block_borders(cpu)
+
+
+def test_far_key(cpu):
+    C.case_far_key(cpu)
+
+
+def test_slow_recurrence_remembers(cpu):
+    C.case_slow_recurrence_remembers(cpu)
