@@ -10,6 +10,9 @@
 //   linear_attention   per head: S <- decay_h S + silu(k) silu(v)^T (S: dk x dv), out = S^T silu(q)
 //   gated_rmsnorm      out = x / rms(x) * weight * sigmoid(gate) * out_scale
 // Gates, decays, the states and the norm run in fp32 for every storage type T of the projections.
+#include <type_traits>
+
+#include "mma_helpers.cuh"
 #include "typed_io.cuh"
 
 namespace sllm {
@@ -199,6 +202,22 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) rglru_scan_tiled_kernel(
     }
 }
 
+// A read-only global load that stays where it is written (a volatile asm is not moved across other volatile asm or barriers): the
+// prefetch of the next token batch must be ISSUED before the current batch is multiplied, not sunk to its first use.
+template <typename T>
+__device__ __forceinline__ float ldf_pinned(const T* p) {
+    if constexpr (sizeof(T) == 4) {
+        float f;
+        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(f) : "l"(p));
+        return f;
+    } else {
+        unsigned short u;
+        asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(u) : "l"(p));
+        if constexpr (std::is_same<T, __nv_bfloat16>::value) return __uint_as_float((unsigned)u << 16);
+        else return __half2float(__ushort_as_half(u));
+    }
+}
+
 // silu of a projection's output.  With 16-bit storage the activation only has to be good to that type's rounding: fast exponential
 // and division; with fp32 storage the accurate ones.
 template <typename T>
@@ -208,38 +227,45 @@ __device__ __forceinline__ float silu_act(float z) {
 }
 
 // Linear attention with a constant decay per head.  The columns of a head's state S [dk, dv] never mix (out[j] = sum_d S[d, j] q[d],
-// S[d, j] <- decay S[d, j] + k[d] v[j]), so a CTA owns LA_COLS columns of one (segment, head): grid (segments, heads,
-// ceil(dv / LA_COLS)), 8 warps.  Lane j: column; warp w: rows w R .. w R + R - 1 of the state, in registers for the whole segment.
-// Tokens are staged LA_TOKENS at a time (silu applied once, rows padded with zeros to 8 R); every warp walks them without a
-// barrier and keeps its partial dot products in registers; the eight partial sums per (token, column) meet in shared memory once
-// per batch.
+// S[d, j] <- decay S[d, j] + k[d] v[j]), so a CTA owns 32 CPT columns of one (segment, head): grid (segments, heads,
+// ceil(dv / (32 CPT))), 8 warps.  Lane j: columns j, j + 32, .. (CPT of them); warp w: rows w R .. w R + R - 1 of the state, in
+// registers for the whole segment.  Tokens are staged LA_TOKENS at a time (silu applied once, rows padded with zeros to 8 R);
+// every warp walks them without a barrier and keeps its partial dot products in registers; the eight partial sums per (token,
+// column) meet in shared memory once per batch.  k and q reach the threads as broadcast reads of shared memory, four rows a read;
+// every read serves 4 CPT fused multiply-adds per lane, and CPT = 4 is where the shared-memory pipe and the FMA pipe balance.
 // Inside a batch the decay is folded into the staged vectors: with U_i = S_start + sum_{j <= i} decay^-(j+1) k_j v_j^T the state
 // after token i is decay^(i+1) U_i, so k_j is staged times decay^-(j+1), q_i times decay^(i+1), the update is ONE fused
 // multiply-add per state entry (plus one for the dot product), and the state is scaled by decay^tokens once per batch.  Eight
 // tokens keep the factors within 2^32 for decay >= 1/16; a smaller decay takes the direct form (decay * S + k v).
-constexpr int LA_COLS = 32;
-constexpr float LA_MIN_FOLDED_DECAY = 0.0625f;
 constexpr int LA_TOKENS = 8;
 constexpr int LA_WARPS = 8;
+constexpr float LA_MIN_FOLDED_DECAY = 0.0625f;
 
-template <typename T, int R>
+// ASYNC: the next batch's raw q / k / v rows travel to shared memory by cp.async (16-byte pieces: needs 16-byte aligned rows, see
+// the launcher) while the current batch is multiplied; otherwise they are prefetched into registers by plain loads.
+template <typename T, int R, int CPT, bool ASYNC>
 __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_kernel(
     const T* __restrict__ q, int64_t q_stride, const T* __restrict__ k, int64_t k_stride, const T* __restrict__ v, int64_t v_stride,
     const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ seg_starts, const int* __restrict__ seq_ids,
     const int* __restrict__ tok_pos, float* __restrict__ out, int H, int dk, int dv) {
     constexpr int DKP = LA_WARPS * R;                                   // padded rows
-    __shared__ __align__(16) float qs[LA_TOKENS][DKP];
-    __shared__ __align__(16) float ks[LA_TOKENS][DKP];
-    __shared__ float vs[LA_TOKENS][LA_COLS];
-    __shared__ float red[LA_WARPS][LA_TOKENS][LA_COLS];
-    __shared__ float fq[LA_TOKENS], fk[LA_TOKENS];                      // decay^(i+1) and its inverse (1 in the direct form)
+    constexpr int COLS = 32 * CPT;
+    extern __shared__ __align__(16) unsigned char la_smem[];
+    float (*qs)[DKP] = reinterpret_cast<float (*)[DKP]>(la_smem);                                   // [LA_TOKENS][DKP]
+    float (*ks)[DKP] = qs + LA_TOKENS;                                                               // [LA_TOKENS][DKP]
+    float (*vs)[COLS] = reinterpret_cast<float (*)[COLS]>(ks + LA_TOKENS);                           // [LA_TOKENS][COLS]
+    float (*red)[LA_TOKENS][COLS] = reinterpret_cast<float (*)[LA_TOKENS][COLS]>(vs + LA_TOKENS);    // [LA_WARPS][LA_TOKENS][COLS]
+    float* fq = reinterpret_cast<float*>(red + LA_WARPS);               // decay^(i+1) ...
+    float* fk = fq + LA_TOKENS;                                         // ... and its inverse (1 in the direct form)
+    T* rawq = reinterpret_cast<T*>(fk + LA_TOKENS);                     // ASYNC only: [LA_TOKENS][dk], [LA_TOKENS][dk], [LA_TOKENS][COLS]
+    T* rawk = rawq + LA_TOKENS * dk;
+    T* rawv = rawk + LA_TOKENS * dk;
     const int b = blockIdx.x, h = blockIdx.y;
     const int t0 = seg_starts[b], n = seg_starts[b + 1] - t0;
     if (n <= 0) return;
     const int seq = seq_ids[b], p0 = tok_pos[t0];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int col = blockIdx.z * LA_COLS + lane;
-    const bool col_ok = col < dv;
+    const int col0 = blockIdx.z * COLS + lane;                          // this thread's columns: col0 + 32 c
     const float lam = decay[h];
     const bool folded = lam >= LA_MIN_FOLDED_DECAY;
     if (tid < LA_TOKENS) {
@@ -248,17 +274,19 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_kernel(
         fk[tid] = 1.f / pw;
     }
     float* st = state + ((int64_t)seq * H + h) * dk * dv;
-    float S[R];
+    float S[R][CPT];
 #pragma unroll
     for (int r = 0; r < R; r++) {
         const int d = warp * R + r;
-        S[r] = (col_ok && d < dk && p0 > 0) ? st[(int64_t)d * dv + col] : 0.f;
+#pragma unroll
+        for (int c = 0; c < CPT; c++)
+            S[r][c] = (col0 + 32 * c < dv && d < dk && p0 > 0) ? st[(int64_t)d * dv + col0 + 32 * c] : 0.f;
     }
     __syncthreads();                                                    // fq / fk
     // raw inputs of one batch, as this thread stages them: NQ entries of q and of k (entry idx = tid + e * 256 of the padded
-    // [LA_TOKENS][DKP] tile), one of v (warp i stages token i's columns)
+    // [LA_TOKENS][DKP] tile), CPT of v (warp i stages token i's columns)
     constexpr int NQ = LA_TOKENS * DKP / (LA_WARPS * 32);
-    float rq[NQ], rk[NQ], rv;
+    float rq[NQ], rk[NQ], rv[CPT];
     auto fetch = [&](int i0) {
         const int nt = min(LA_TOKENS, n - i0);
 #pragma unroll
@@ -268,82 +296,131 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_kernel(
             rq[e] = 0.f; rk[e] = 0.f;
             if (i < nt && d < dk) {
                 const int64_t t = t0 + i0 + i;
-                rq[e] = ldf(q + t * q_stride + (int64_t)h * dk + d);
-                rk[e] = ldf(k + t * k_stride + (int64_t)h * dk + d);
+                rq[e] = ldf_pinned(q + t * q_stride + (int64_t)h * dk + d);
+                rk[e] = ldf_pinned(k + t * k_stride + (int64_t)h * dk + d);
             }
         }
-        rv = (warp < nt && col_ok) ? ldf(v + (int64_t)(t0 + i0 + warp) * v_stride + (int64_t)h * dv + col) : 0.f;
+#pragma unroll
+        for (int c = 0; c < CPT; c++)
+            rv[c] = (warp < nt && col0 + 32 * c < dv) ? ldf_pinned(v + (int64_t)(t0 + i0 + warp) * v_stride + (int64_t)h * dv + col0 + 32 * c) : 0.f;
     };
-    fetch(0);
+    // ASYNC: 16-byte pieces of the batch's rows, round-robin over the threads
+    constexpr int PIECE = 16 / (int)sizeof(T);                          // elements per piece
+    auto issue = [&](int i0) {
+        const int nt = min(LA_TOKENS, n - i0);
+        const int cq = dk / PIECE;
+        for (int idx = tid; idx < nt * cq; idx += LA_WARPS * 32) {
+            const int i = idx / cq, ch = idx - i * cq;
+            const int64_t t = t0 + i0 + i;
+            cp_async16(smem_u32(rawq + i * dk + ch * PIECE), q + t * q_stride + (int64_t)h * dk + ch * PIECE);
+            cp_async16(smem_u32(rawk + i * dk + ch * PIECE), k + t * k_stride + (int64_t)h * dk + ch * PIECE);
+        }
+        constexpr int CV = COLS / PIECE;
+        for (int idx = tid; idx < nt * CV; idx += LA_WARPS * 32) {
+            const int i = idx / CV, ch = idx - i * CV;
+            const int c0 = blockIdx.z * COLS + ch * PIECE;
+            if (c0 < dv)                                                // dv is a multiple of PIECE: the piece is inside the row
+                cp_async16(smem_u32(rawv + i * COLS + ch * PIECE), v + (int64_t)(t0 + i0 + i) * v_stride + (int64_t)h * dv + c0);
+        }
+        cp_async_commit();
+    };
+    if constexpr (ASYNC) issue(0); else fetch(0);
     for (int i0 = 0; i0 < n; i0 += LA_TOKENS) {
         const int nt = min(LA_TOKENS, n - i0);
         // stage the batch: silu(q), silu(k) (zeros from dk on), silu(v) of this CTA's columns (silu(0) = 0 keeps the padding)
+        if constexpr (ASYNC) {
+            cp_async_wait<0>();
+            __syncthreads();                                            // the raw rows have landed (every thread's pieces)
 #pragma unroll
-        for (int e = 0; e < NQ; e++) {
-            const int idx = tid + e * (LA_WARPS * 32);
-            const int i = idx / DKP, d = idx - i * DKP;
-            qs[i][d] = silu_act<T>(rq[e]) * fq[i];
-            ks[i][d] = silu_act<T>(rk[e]) * fk[i];
+            for (int e = 0; e < NQ; e++) {
+                const int idx = tid + e * (LA_WARPS * 32);
+                const int i = idx / DKP, d = idx - i * DKP;
+                const bool live = i < nt && d < dk;
+                qs[i][d] = live ? silu_act<T>(ldf(rawq + i * dk + d)) * fq[i] : 0.f;
+                ks[i][d] = live ? silu_act<T>(ldf(rawk + i * dk + d)) * fk[i] : 0.f;
+            }
+#pragma unroll
+            for (int c = 0; c < CPT; c++)
+                vs[warp][lane + 32 * c] = (warp < nt && col0 + 32 * c < dv) ? silu_act<T>(ldf(rawv + warp * COLS + lane + 32 * c)) : 0.f;
+            __syncthreads();                                            // staged; the raw rows may be overwritten
+            if (i0 + LA_TOKENS < n) issue(i0 + LA_TOKENS);              // in flight while this batch is multiplied
+        } else {
+#pragma unroll
+            for (int e = 0; e < NQ; e++) {
+                const int idx = tid + e * (LA_WARPS * 32);
+                const int i = idx / DKP, d = idx - i * DKP;
+                qs[i][d] = silu_act<T>(rq[e]) * fq[i];
+                ks[i][d] = silu_act<T>(rk[e]) * fk[i];
+            }
+#pragma unroll
+            for (int c = 0; c < CPT; c++) vs[warp][lane + 32 * c] = silu_act<T>(rv[c]);
+            if (i0 + LA_TOKENS < n) fetch(i0 + LA_TOKENS);    // in flight while this batch is multiplied
+            __syncthreads();
         }
-        vs[warp][lane] = silu_act<T>(rv);
-        if (i0 + LA_TOKENS < n) fetch(i0 + LA_TOKENS);        // in flight while this batch is multiplied
-        __syncthreads();
-        float part[LA_TOKENS];
+        // one token after the other; `fold` is a compile-time flag so that the loops hold fused multiply-adds only
+        auto multiply = [&](auto fold) {
+            constexpr bool FOLD = decltype(fold)::value;
 #pragma unroll
-        for (int i = 0; i < LA_TOKENS; i++) {
-            part[i] = 0.f;
-            if (i < nt) {                                               // uniform over the CTA
-                const float vj = vs[i][lane];
-                float acc = 0.f;
-                if (folded) {                                           // uniform over the CTA
+            for (int i = 0; i < LA_TOKENS; i++) {
+                float part[CPT];
 #pragma unroll
-                    for (int r = 0; r < R; r += 4) {
-                        const float4 k4 = *reinterpret_cast<const float4*>(&ks[i][warp * R + r]);
-                        const float4 q4 = *reinterpret_cast<const float4*>(&qs[i][warp * R + r]);
-                        S[r] = fmaf(k4.x, vj, S[r]);         acc = fmaf(S[r], q4.x, acc);
-                        S[r + 1] = fmaf(k4.y, vj, S[r + 1]); acc = fmaf(S[r + 1], q4.y, acc);
-                        S[r + 2] = fmaf(k4.z, vj, S[r + 2]); acc = fmaf(S[r + 2], q4.z, acc);
-                        S[r + 3] = fmaf(k4.w, vj, S[r + 3]); acc = fmaf(S[r + 3], q4.w, acc);
-                    }
-                } else {
+                for (int c = 0; c < CPT; c++) part[c] = 0.f;
+                if (i < nt) {                                           // uniform over the CTA
+                    float vj[CPT];
+#pragma unroll
+                    for (int c = 0; c < CPT; c++) vj[c] = vs[i][lane + 32 * c];
 #pragma unroll
                     for (int r = 0; r < R; r += 4) {
                         const float4 k4 = *reinterpret_cast<const float4*>(&ks[i][warp * R + r]);
                         const float4 q4 = *reinterpret_cast<const float4*>(&qs[i][warp * R + r]);
-                        S[r] = lam * S[r] + k4.x * vj;         acc += S[r] * q4.x;
-                        S[r + 1] = lam * S[r + 1] + k4.y * vj; acc += S[r + 1] * q4.y;
-                        S[r + 2] = lam * S[r + 2] + k4.z * vj; acc += S[r + 2] * q4.z;
-                        S[r + 3] = lam * S[r + 3] + k4.w * vj; acc += S[r + 3] * q4.w;
+                        const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+#pragma unroll
+                            for (int c = 0; c < CPT; c++) {
+                                if constexpr (FOLD) S[r + e][c] = fmaf(kk[e], vj[c], S[r + e][c]);
+                                else S[r + e][c] = fmaf(lam, S[r + e][c], kk[e] * vj[c]);
+                                part[c] = fmaf(S[r + e][c], qq[e], part[c]);
+                            }
+                        }
                     }
                 }
-                part[i] = acc;
+#pragma unroll
+                for (int c = 0; c < CPT; c++) red[warp][i][lane + 32 * c] = part[c];
             }
-        }
-        if (folded) {
-            const float back = fq[nt - 1];                              // U -> S = decay^tokens U
+            if constexpr (FOLD) {
+                const float back = fq[nt - 1];                          // U -> S = decay^tokens U
 #pragma unroll
-            for (int r = 0; r < R; r++) S[r] *= back;
-        }
+                for (int r = 0; r < R; r++)
 #pragma unroll
-        for (int i = 0; i < LA_TOKENS; i++) red[warp][i][lane] = part[i];
+                    for (int c = 0; c < CPT; c++) S[r][c] *= back;
+            }
+        };
+        if (folded) multiply(std::true_type{});                         // uniform over the CTA
+        else multiply(std::false_type{});
         __syncthreads();                    // partial sums visible; qs / ks / vs are done with and may be staged again
         {
             const int i = warp;                                         // warp i adds up token i
-            if (i < nt && col_ok) {
-                float o = 0.f;
+            if (i < nt) {
 #pragma unroll
-                for (int w = 0; w < LA_WARPS; w++) o += red[w][i][lane];
-                out[(int64_t)(t0 + i0 + i) * ((int64_t)H * dv) + (int64_t)h * dv + col] = o;
+                for (int c = 0; c < CPT; c++) {
+                    if (col0 + 32 * c < dv) {
+                        float o = 0.f;
+#pragma unroll
+                        for (int w = 0; w < LA_WARPS; w++) o += red[w][i][lane + 32 * c];
+                        out[(int64_t)(t0 + i0 + i) * ((int64_t)H * dv) + (int64_t)h * dv + col0 + 32 * c] = o;
+                    }
+                }
             }
         }
         // the next batch writes `red` only after its own first barrier, which every warp reaches after this read
     }
-    if (col_ok) {
 #pragma unroll
-        for (int r = 0; r < R; r++) {
-            const int d = warp * R + r;
-            if (d < dk) st[(int64_t)d * dv + col] = S[r];
-        }
+    for (int r = 0; r < R; r++) {
+        const int d = warp * R + r;
+#pragma unroll
+        for (int c = 0; c < CPT; c++)
+            if (col0 + 32 * c < dv && d < dk) st[(int64_t)d * dv + col0 + 32 * c] = S[r][c];
     }
 }
 
@@ -365,21 +442,53 @@ __global__ void __launch_bounds__(256) gated_rmsnorm_kernel(const float* __restr
     }
 }
 
+template <typename T, int R, int CPT, bool ASYNC>
+static void launch_linear_attention_as(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
+                                       int64_t v_stride, const void* decay, void* state, const void* seg_starts, const void* seq_ids,
+                                       const void* tok_pos, void* out, int num_segs, int H, int dk, int dv, cudaStream_t stream) {
+    static unsigned long long attr_mask = 0;
+    auto kern = linear_attention_kernel<T, R, CPT, ASYNC>;
+    if (first_use_on_this_device(attr_mask)) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    constexpr int DKP = LA_WARPS * R, COLS = 32 * CPT;
+    size_t smem = sizeof(float) * (2 * LA_TOKENS * DKP + LA_TOKENS * COLS + LA_WARPS * LA_TOKENS * COLS + 2 * LA_TOKENS);
+    if (ASYNC) smem += sizeof(T) * (size_t)LA_TOKENS * (2 * dk + COLS);
+    kern<<<dim3((unsigned)num_segs, (unsigned)H, (unsigned)cdiv(dv, COLS)), LA_WARPS * 32, smem, stream>>>(
+        (const T*)q, q_stride, (const T*)k, k_stride, (const T*)v, v_stride, (const float*)decay, (float*)state,
+        (const int*)seg_starts, (const int*)seq_ids, (const int*)tok_pos, (float*)out, H, dk, dv);
+}
+
 template <typename T>
 static int launch_linear_attention(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v, int64_t v_stride,
                                    const void* decay, void* state, const void* seg_starts, const void* seq_ids, const void* tok_pos,
                                    void* out, int num_segs, int H, int dk, int dv, cudaStream_t stream) {
-    const int rows = cdiv(dk, LA_WARPS);                                // state rows per warp
-    const dim3 grid((unsigned)num_segs, (unsigned)H, (unsigned)cdiv(dv, LA_COLS));
-#define LA(R)                                                                                                                  \
-    linear_attention_kernel<T, R><<<grid, LA_WARPS * 32, 0, stream>>>((const T*)q, q_stride, (const T*)k, k_stride, (const T*)v,  \
-        v_stride, (const float*)decay, (float*)state, (const int*)seg_starts, (const int*)seq_ids, (const int*)tok_pos,         \
-        (float*)out, H, dk, dv)
-    if (rows <= 4) LA(4);                                               // R is a multiple of 4: whole float4 reads, R / 4 staged entries per thread
-    else if (rows <= 8) LA(8);
-    else if (rows <= 16) LA(16);
-    else if (rows <= 32) LA(32);
-    else LA(64);
+    const int rows = cdiv(dk, LA_WARPS);                                // state rows per warp, rounded up to 4, 8, 16, 32 or 64
+    // cp.async moves 16-byte pieces: every head's row of q, k and v must start on a 16-byte boundary and be whole pieces
+    const int piece = 16 / (int)sizeof(T);
+    const bool aligned = dk % piece == 0 && dv % piece == 0 && q_stride % piece == 0 && k_stride % piece == 0 &&
+                         v_stride % piece == 0 && (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0;
+    // columns per thread (CPT): more columns make every broadcast read of k and q serve more multiply-adds, but leave fewer
+    // CTAs; take the widest slice that still gives every SM a CTA (R * CPT state registers and the shared memory allowing)
+    int num_sms = 0;
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, current_device());
+    int cpt = 1;
+    const int64_t units = (int64_t)num_segs * H;
+    if (dv > 64 && units * cdiv(dv, 128) >= num_sms) cpt = 4;
+    else if (dv > 32 && units * cdiv(dv, 64) >= num_sms) cpt = 2;
+#define LA(R, CPT)                                                                                                             \
+    do {                                                                                                                       \
+        if (aligned) launch_linear_attention_as<T, R, CPT, true>(q, q_stride, k, k_stride, v, v_stride, decay, state, seg_starts, \
+                                                                 seq_ids, tok_pos, out, num_segs, H, dk, dv, stream);           \
+        else launch_linear_attention_as<T, R, CPT, false>(q, q_stride, k, k_stride, v, v_stride, decay, state, seg_starts,       \
+                                                          seq_ids, tok_pos, out, num_segs, H, dk, dv, stream);                  \
+    } while (0)
+#define LA_BY_CPT(R, MAXC)                                                                                                     \
+    do { if (cpt >= 4 && MAXC >= 4) LA(R, (MAXC >= 4 ? 4 : MAXC)); else if (cpt >= 2 && MAXC >= 2) LA(R, 2); else LA(R, 1); } while (0)
+    if (rows <= 4) LA_BY_CPT(4, 4);
+    else if (rows <= 8) LA_BY_CPT(8, 4);
+    else if (rows <= 16) LA_BY_CPT(16, 4);
+    else if (rows <= 32) LA_BY_CPT(32, 2);
+    else LA_BY_CPT(64, 1);
+#undef LA_BY_CPT
 #undef LA
     return check_launch("linear_attention");
 }
@@ -447,7 +556,7 @@ int sllm_rglru_scan(const void* u, const void* gates, int blocks, const void* yb
 int sllm_linear_attention(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v, int64_t v_stride,
                           const void* decay, void* state, const void* seg_starts, const void* seq_ids, const void* tok_pos,
                           void* out, int num_segs, int num_heads, int dk, int dv, sllm_dtype_t dtype, sllm_stream_t stream) {
-    SLLM_REQUIRE(num_segs >= 0 && num_heads > 0 && dk > 0 && dv > 0 && dk <= 64 * LA_WARPS && cdiv(dv, LA_COLS) <= 65535,
+    SLLM_REQUIRE(num_segs >= 0 && num_heads > 0 && dk > 0 && dv > 0 && dk <= 64 * LA_WARPS && cdiv(dv, 32) <= 65535,
                  "linear_attention: bad shape (dk %d <= %d, dv %d)", dk, 64 * LA_WARPS, dv);
     if (num_segs == 0) return 0;
     SLLM_REQUIRE(q && k && v && decay && state && seg_starts && seq_ids && tok_pos && out, "linear_attention: null pointer");
