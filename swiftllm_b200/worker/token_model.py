@@ -136,7 +136,10 @@ class TokenBatchModel(PagedModelBase):
         useable_memory = total_memory * self.engine_config.gpu_mem_utilization
         if useable_memory < peak_memory:
             raise RuntimeError(f"Peak memory {peak_memory/GB:.2f} GB exceeds usable memory {useable_memory/GB:.2f} GB")
-        num_gpu_blocks = math.floor((useable_memory - peak_memory) / (self.engine_config.block_size * self._kvslot_bytes()))
+        # a model without caching layers (recurrent mixers only) still needs blocks for the positions' bookkeeping: count them
+        # as one byte per token
+        num_gpu_blocks = math.floor((useable_memory - peak_memory) / (self.engine_config.block_size * max(1, self._kvslot_bytes())))
+        num_gpu_blocks = min(num_gpu_blocks, self.engine_config.max_seqs_in_block_table * self.engine_config.max_blocks_per_seq)
         torch.cuda.empty_cache()
         return num_gpu_blocks
 
