@@ -142,10 +142,10 @@ def _arch_models(sz, dtype, only=None):
     # Buzarax: layers alternate [softmax attention (heads / 4 KV heads, 128 + 128 per head) beside linear attention (128 x 128
     # state per head)] and [gated linear recurrence of the model's width]; one dense feed-forward, the others 16 / 32 experts
     attn = {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
-            "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+            "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}
     lin = {"heads": H, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5.0 - 3.0 * h / max(1, H - 1)) for h in range(H)]}
     buz_moe = {"kind": "moe", "expert": {"ff": sz["eff"]}, "router": {"experts": sz["experts"], "top": sz["top"]}}
-    buz_layers = [{"type": "parallel", "mixer": {"left": attn, "right": lin, "left_scale": 0.6, "right_scale": 1.1},
+    buz_layers = [{"type": "parallel", "mixer": {"left": attn, "right": lin, "left_scale": 0.5, "right_scale": 1.0},
                    "mlp": {"kind": "dense", "ff": sz["ff"], "limit": 7.0} if i == 0 else buz_moe} if i % 2 == 0 else
                   {"type": "rglru", "mixer": {"width": W, "blocks": H, "conv": 4}, "mlp": buz_moe} for i in range(sz["layers"])]
     buz = {"architecture": "Buzarax", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,

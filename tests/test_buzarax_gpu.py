@@ -44,7 +44,7 @@ def _schedule(lens, plan):
 
 # ---------------------------------------------------------------- kernels alone
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("C_,blocks,K", [(24, 3, 4), (33, 11, 1), (20, 1, 2), (256, 4, 4), (130, 2, 8)])
+@pytest.mark.parametrize("C_,blocks,K", [(24, 3, 4), (33, 11, 1), (20, 1, 2), (192, 6, 3), (130, 2, 8)])
 def test_convolution_and_gated_recurrence(dtype, C_, blocks, K):
     """Two sequences in rows 2 and 0 of the state tensors (which start full of junk), fed in portions down to one token, some of
     them long enough for the tiled scan; against the plain loops on each whole sequence."""
@@ -98,7 +98,7 @@ def test_convolution_and_gated_recurrence(dtype, C_, blocks, K):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,dk,dv", [(3, 5, 7), (1, 9, 4), (2, 40, 36), (4, 12, 3), (6, 64, 32), (2, 128, 128), (1, 16, 200)])
+@pytest.mark.parametrize("H,dk,dv", [(3, 5, 7), (1, 9, 4), (2, 40, 36), (4, 12, 3), (5, 48, 80), (2, 128, 128), (1, 16, 200), (2, 24, 64)])
 def test_linear_attention_state_through_portions(dtype, H, dk, dv):
     from swiftllm_b200.worker.kernels.recurrent import linear_attention
     g = torch.Generator().manual_seed(H * dk + dv)
@@ -240,7 +240,7 @@ def test_silu_gated_experts_scaled(dtype):
     assert bool((got.cpu().view(T, E, ff)[w == 0] == 0).all())
 
 
-@pytest.mark.parametrize("H,G,dk,dv,dims,cap", [(8, 2, 32, 16, 32, 5.0), (6, 1, 64, 64, 16, 0.0), (4, 4, 96, 96, 48, 20.0),
+@pytest.mark.parametrize("H,G,dk,dv,dims,cap", [(8, 2, 32, 16, 32, 5.0), (6, 1, 64, 64, 16, 0.0), (6, 3, 112, 80, 56, 12.0),
                                                 (12, 4, 48, 80, 0, 3.0), (4, 2, 128, 128, 128, 30.0)])
 def test_attention_options_tensor_core_and_cuda_core_agree(H, G, dk, dv, dims, cap):
     """Halves rotary, unit-RMS queries and keys, capped scores, turned values, a factor on the output, no window: the same mixed
@@ -256,7 +256,7 @@ def test_attention_options_tensor_core_and_cuda_core_agree(H, G, dk, dv, dims, c
         for b in range((n + bs - 1) // bs):
             table[s, b] = perm.pop()
     table = table.to(DEV)
-    opt = WA.AttnOptions(pair_halves=True, qk_norm_eps=1e-6, softcap=cap, out_scale=0.6)
+    opt = WA.AttnOptions(pair_halves=True, qk_norm_eps=1e-6, softcap=cap, out_scale=0.75)
 
     def angles(pos, n, base=100.0):
         a = torch.tensor(pos, dtype=torch.float64)[:, None] * torch.tensor([base ** (-2.0 * i / n) for i in range(n // 2)],
