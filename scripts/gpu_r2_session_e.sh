@@ -14,10 +14,9 @@ done
 echo "== (while the reference compiles) GPU test suite (the KV-profile test is run later: the reference processes hold 72 GB now)"
 timeout 900 python -m pytest tests -m gpu -q -p no:cacheprovider --maxfail=5 --deselect tests/test_model_gpu.py::test_profile_num_blocks_and_exhaustion > gpurun_out/pytest_all_r2e.log 2>&1; echo "rc=$?"; tail -4 gpurun_out/pytest_all_r2e.log | cut -c1-300
 grep -h "golden_trace_vs_exact\|golden_trace_summary" gpurun_out/parity_log.jsonl | tail -8 | cut -c1-250
-echo "== ncu source-level capture of prefill_attn_tc_kernel (8 x 4096)"
-timeout 600 ncu --set full --import-source on --clock-control none -k regex:prefill_attn_tc_kernel --launch-skip 2 --launch-count 1 -f -o gpurun_out/r2_prefill_tc python scripts/prefill_one.py > gpurun_out/ncu_prefill.log 2>&1; echo "rc=$?"; tail -2 gpurun_out/ncu_prefill.log | cut -c1-200
+echo "== ncu counters of prefill_attn_tc_kernel (8 x 4096)"
+timeout 600 ncu --set full --clock-control none -k regex:prefill_attn_tc_kernel --launch-skip 2 --launch-count 1 -f -o gpurun_out/r2_prefill_tc python scripts/prefill_one.py > gpurun_out/ncu_prefill.log 2>&1; echo "rc=$?"; tail -2 gpurun_out/ncu_prefill.log | cut -c1-200
 ncu -i gpurun_out/r2_prefill_tc.ncu-rep --page raw --csv > gpurun_out/r2_prefill_tc_raw.csv 2>/dev/null
-ncu -i gpurun_out/r2_prefill_tc.ncu-rep --page source --csv > gpurun_out/r2_prefill_tc_source.csv 2>/dev/null
 ls -la gpurun_out/r2_prefill_tc* | cut -c1-200
 echo "== waiting for the reference's Triton compiles"
 wait
@@ -48,6 +47,6 @@ grep "^\[bench" gpurun_out/bench_n1_full.err | cut -c1-200; grep -v "^\[bench" g
 echo "== ncu: the reference's phase-1 kernel (time, DRAM bytes), fp16 as shipped, warm cache"
 REF_STEPS=1 REF_WARMUP=0 timeout 400 ncu --metrics gpu__time_duration.sum,dram__bytes_read.sum,dram__bytes_write.sum --clock-control none --csv -k regex:_fwd_paged_attention_phase --launch-skip 70 --launch-count 6 python scripts/ref_triton_bench.py > gpurun_out/ncu_ref_phase1.csv 2> gpurun_out/ncu_ref_phase1.err; echo "rc=$?"
 grep -E "paged_attention" gpurun_out/ncu_ref_phase1.csv | cut -d, -f5,12- | head -20 | cut -c1-200
-gzip -f gpurun_out/r2_prefill_tc_source.csv gpurun_out/r2_prefill_tc_raw.csv 2>/dev/null
+gzip -f gpurun_out/r2_prefill_tc_raw.csv 2>/dev/null
 sz=$(du -sm gpurun_out | cut -f1); echo "gpurun_out: ${sz} MiB"
 if [ "$sz" -gt 58 ]; then echo "dropping the .ncu-rep (csv exports kept)"; rm -f gpurun_out/r2_prefill_tc.ncu-rep; du -sm gpurun_out; fi
