@@ -241,9 +241,11 @@ int sllm_moe_route_grouped(const void* logits, void* weights, int64_t num_tokens
 /* Clamped gated-linear-unit experts.  u [T, 2 * cols] (dtype): per expert [gate (ff) | up (ff)], then a shared expert's
  * [gate (shared_ff) | up (shared_ff)]; y [T, cols] (dtype), cols = experts * ff + shared_ff.  With g = min(gate, limit),
  * v = clamp(up, -limit, limit): y = g * sigmoid(alpha * g) * (v + 1) * weights[t, e]; the shared expert uses shared_limit and
- * weight 1.  experts or shared_ff may be 0 (weights may then be NULL / no shared part). */
+ * weight 1, or with shared_gated = 1 the weight weights[t, experts] (weights then has experts + 1 columns).  experts or
+ * shared_ff may be 0 (weights may then be NULL / no shared part). */
 int sllm_moe_clamped_glu_scale(const void* u, const void* weights, void* y, int64_t num_tokens, int experts, int ff, float limit,
-                               int shared_ff, float shared_limit, float alpha, sllm_dtype_t dtype, sllm_stream_t stream);
+                               int shared_ff, float shared_limit, float alpha, int shared_gated, sllm_dtype_t dtype,
+                               sllm_stream_t stream);
 /* u [T, experts * ff] (dtype) = relu(u)^2 * weights[t, column / ff]: experts a token does not use contribute exact zeros. */
 int sllm_moe_relu2_scale_inplace(void* u, const void* weights, int64_t num_tokens, int experts, int ff, sllm_dtype_t dtype,
                                  sllm_stream_t stream);
@@ -279,12 +281,16 @@ int sllm_latent_attention(const void* q_lat, int64_t q_lat_stride_t, int64_t q_l
  * Options shared with window_attention: pair_halves = 1 pairs entry i with i + rot_dims / 2 (0: entries 2i and 2i + 1);
  * qk_norm_eps >= 0 divides every rotated key / query head by sqrt(mean of its squares + eps) (< 0: off); vcos / vsin (fp32
  * [T, dv / 2], or NULL) turn the value of every head by the token's position before it is stored, and window_attention turns
- * each head's output back by the query's position. */
+ * each head's output back by the query's position.
+ * knorm_w / qnorm_w (fp32 [dk], or NULL): every key / query head is first RMS-normed, x / sqrt(mean(x^2) + prenorm_eps) * w,
+ * BEFORE it turns.  vshare >= 1: `vshare` neighbouring key heads share one value head (value head = key head / vshare): v is
+ * [T, num_kv_heads / vshare * dv] and the cache row [num_kv_heads * dk | num_kv_heads / vshare * dv]. */
 int sllm_window_kv_store(const void* k, int64_t k_row_stride, const void* v, int64_t v_row_stride, const void* cosb,
                          const void* sinb, const void* tok_seq, const void* tok_pos, const void* block_table,
                          int max_blocks_per_seq, void* cache, int n_slots, int slot, int block_size, int64_t num_tokens,
                          int num_kv_heads, int dk, int dv, int rot_dims, int pair_halves, float qk_norm_eps, const void* vcos,
-                         const void* vsin, sllm_dtype_t dtype, sllm_stream_t stream);
+                         const void* vsin, const void* knorm_w, float prenorm_eps, int vshare, sllm_dtype_t dtype,
+                         sllm_stream_t stream);
 /* window_attention: per token i at position p and query head h (key/value head h / (num_heads / num_kv_heads)), over the cached
  * positions max(0, p - window + 1) .. p (all of 0 .. p when window <= 0):
  *   out[i, h, :dv] = sigmoid(gate[i, h, :dv]) * sum_j p_j v_j,   p_j = exp(s_j) / (sink + sum_j' exp(s_j')),
@@ -294,15 +300,24 @@ int sllm_window_kv_store(const void* k, int64_t k_row_stride, const void* v, int
  * tokens are grouped into CTAs; any value in 0 .. num_tokens gives the same result).
  * 16-bit dtypes with dk, dv multiples of 16 and <= 128 run on tensor cores (mma.sync over tokens x heads of a key/value group);
  * other shapes and SLLM_F32 run the fp32 CUDA-core kernel.  sllm_window_attention_set_simt(1) forces the latter (returns the
- * old setting).  softcap > 0: s_j <- softcap * tanh(s_j / softcap); out_scale multiplies the output. */
+ * old setting).  softcap > 0: s_j <- softcap * tanh(s_j / softcap); out_scale multiplies the output.
+ * chunk > 0: only keys at positions >= floor(p / chunk) * chunk are seen.  out_f32 = 1: `out` is fp32 for every dtype (its row
+ * stride counts floats; no turned values then). */
 int sllm_window_attention_set_simt(int on);
 int sllm_window_attention(const void* q, int64_t q_stride_t, const void* cosb, const void* sinb, const void* gate,
                           int64_t gate_stride_t, const void* cache, int n_slots, int slot, int block_size,
                           const void* block_table, int max_blocks_per_seq, const void* tok_seq, const void* tok_pos, void* out,
                           int64_t out_stride_t, int64_t num_tokens, int64_t num_prefill_tokens, int num_heads, int num_kv_heads,
                           int dk, int dv, int rot_dims, int window, float scale, int sink, int pair_halves, float qk_norm_eps,
-                          float softcap, const void* vcos, const void* vsin, float out_scale, sllm_dtype_t dtype,
-                          sllm_stream_t stream);
+                          float softcap, const void* vcos, const void* vsin, float out_scale, const void* qnorm_w,
+                          float prenorm_eps, int chunk, int vshare, int out_f32, sllm_dtype_t dtype, sllm_stream_t stream);
+/* diff_combine: a fp32 [T, num_kv_heads, 2, num_heads / num_kv_heads, dv] - the outputs of two score maps per head over the same
+ * values (window_attention with vshare = 2, 2 * num_heads queries ordered [key/value head][map][head of the group], out_f32).
+ * out[t, h] = o / sqrt(mean(o^2) + eps) * factor * sigmoid(gate[t, h]) with o = a[map 0] - lambda * a[map 1]; gate logits
+ * [T, num_heads * dv] or NULL; out [T, num_heads * dv] (dtype), heads in their natural order; row strides in elements. */
+int sllm_diff_combine(const void* a, const void* gate, int64_t gate_stride_t, void* out, int64_t out_stride_t, int64_t num_tokens,
+                      int num_heads, int num_kv_heads, int dv, float lambda, float eps, float factor, sllm_dtype_t dtype,
+                      sllm_stream_t stream);
 
 /* ---- Sequential blocks on an fp32 residual stream whose sublayer OUTPUTS are normalised (new, stream_ops.cu).
  * embed_pair_hash: x[t] (fp32) = embed[tokens[t]] + pairs[row], row = (previous * mul_prev + token * mul_cur) mod buckets with
@@ -352,6 +367,43 @@ int sllm_linear_attention(const void* q, int64_t q_stride, const void* k, int64_
                           void* out, int num_segs, int num_heads, int dk, int dv, sllm_dtype_t dtype, sllm_stream_t stream);
 int sllm_gated_rmsnorm(const void* x, const void* weight, const void* gate, int64_t gate_stride, float eps, float out_scale,
                        void* out, int64_t out_stride, int64_t num_tokens, int n, sllm_dtype_t dtype, sllm_stream_t stream);
+
+/* ---- Sandwich blocks: x <- x + mult * norm_b(sublayer(norm_a(x))) with RMS norms over `groups` equal consecutive parts of a row
+ * (new, sandwich_ops.cu).  group_norm_add_norm: with y (dtype [T, width]) x (fp32, in place) += mult * y / rms_g(y) * wb; with
+ * wn, n_out (fp32) = x / rms_g(x) * wn of the updated x; either half may be left out (NULL).  group_norm_cast: out (dtype) =
+ * x / rms_g(x) * w.  stream_add: x += a (fp32 [T, width] or NULL) + v (fp32 [width] or NULL).
+ * gelu_glu: u [T, 2 ff] = [gate | up] -> y [T, ff] = gelu_tanh(gate) * up.
+ * moe_route_softmax: logits fp32 [T, experts (+ 1 when gated)] -> weights of the same shape: s = softmax over the experts, the
+ * `top` largest s (equal values: the lower index) keep s, the others 0; gated: the last column becomes its sigmoid. */
+int sllm_group_norm_add_norm(void* x, const void* y, const void* wb, float mult, const void* wn, void* n_out, float eps,
+                             int64_t num_tokens, int width, int groups, sllm_dtype_t dtype, sllm_stream_t stream);
+int sllm_group_norm_cast(const void* x, const void* w, void* out, float eps, int64_t num_tokens, int width, int groups,
+                         sllm_dtype_t dtype, sllm_stream_t stream);
+int sllm_stream_add(void* x, const void* a, const void* v, int64_t num_tokens, int width, sllm_stream_t stream);
+int sllm_gelu_glu(const void* u, void* y, int64_t num_tokens, int ff, sllm_dtype_t dtype, sllm_stream_t stream);
+int sllm_moe_route_softmax(const void* logits, void* weights, int64_t num_tokens, int experts, int top, int gated,
+                           sllm_stream_t stream);
+
+/* ---- Per-channel recurrences with per-sequence state (new, scan_ops.cu); segments as for the recurrent mixers above.
+ * short_conv: out[t, c] = act(bias[c] + sum_k w[c, taps - 1 - k] * xin[t - k, c]) (+ xin[t, c] when add_input); w, bias fp32;
+ * xin and tail ([rows, taps - 1, channels]) of in_dtype (SLLM_F32 or out_dtype); act_silu = 1: SiLU.  conv_tail_update moves
+ * the tail on by the segments' inputs and runs after every reader of the old tail.
+ * mingru_scan: proj [T, 3 channels] rows [z logits | candidate pre-activations u | gate pre-activations g] (row stride in
+ * elements); z = sigmoid, c = u + 1/2 (u >= 0) | sigmoid(u); S <- (1 - z) S + z c; out = S * silu(g); state fp32 [rows, channels].
+ * selective_scan: x, z dtype [T, channels]; dt [T, channels] step logits (fp32 when dt_f32, else dtype); bc rows hold B at
+ * column b_off and C at c_off (`states` each); A fp32 [channels, states]; dt = softplus(dt + dt_bias);
+ * S[c, n] <- exp(dt A) S + dt x B[n]; out = (sum_n S C[n] + D x) * silu(z); state fp32 [rows, channels, states]; states <= 256. */
+int sllm_short_conv(const void* xin, int64_t xin_stride, sllm_dtype_t in_dtype, const void* w, const void* bias, const void* tail,
+                    const void* tok_seq, const void* tok_pos, void* out, sllm_dtype_t out_dtype, int64_t num_tokens,
+                    int64_t num_prefill_tokens, int channels, int taps, int add_input, int act_silu, sllm_stream_t stream);
+int sllm_conv_tail_update(const void* xin, int64_t xin_stride, void* tail, const void* seg_starts, const void* seq_ids,
+                          const void* tok_pos, int num_segs, int channels, int taps, sllm_dtype_t dtype, sllm_stream_t stream);
+int sllm_mingru_scan(const void* proj, int64_t proj_stride, void* state, const void* seg_starts, const void* seq_ids,
+                     const void* tok_pos, void* out, int num_segs, int channels, sllm_dtype_t dtype, sllm_stream_t stream);
+int sllm_selective_scan(const void* x, int64_t x_stride, const void* dt, int64_t dt_stride, int dt_f32, const void* dt_bias,
+                        const void* A, const void* bc, int64_t bc_stride, int b_off, int c_off, const void* D, const void* z,
+                        int64_t z_stride, void* state, const void* seg_starts, const void* seq_ids, const void* tok_pos, void* out,
+                        int num_segs, int channels, int states, sllm_dtype_t dtype, sllm_stream_t stream);
 
 #ifdef __cplusplus
 }

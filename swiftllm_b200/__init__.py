@@ -9,13 +9,15 @@ The control plane (Engine, Scheduler, API server, tokenizer) is out of scope; th
 drive this LlamaModel.
 """
 from swiftllm_b200.engine_config import EngineConfig
-from swiftllm_b200.model_config import BupozenModelConfig, BuzaraxModelConfig, LlamaModelConfig, RivudraModelConfig
+from swiftllm_b200.model_config import (BupozenModelConfig, BuzaraxModelConfig, LlamaModelConfig, NaforaxModelConfig,
+                                        RivudraModelConfig)
 from swiftllm_b200.registry import create_model, load_model_config
 from swiftllm_b200.worker.bupozen_model import BupozenModel
 from swiftllm_b200.worker.buzarax_model import BuzaraxModel
 from swiftllm_b200.worker.model import LlamaModel
+from swiftllm_b200.worker.naforax_model import NaforaxModel
 from swiftllm_b200.worker.rivudra_model import RivudraModel
 
 __all__ = ["EngineConfig", "LlamaModelConfig", "LlamaModel", "BupozenModelConfig", "BupozenModel", "RivudraModelConfig", "RivudraModel",
-           "BuzaraxModelConfig", "BuzaraxModel", "create_model",
+           "BuzaraxModelConfig", "BuzaraxModel", "NaforaxModelConfig", "NaforaxModel", "create_model",
            "load_model_config"]

@@ -49,16 +49,27 @@ SIGNATURES = {
     "sllm_relu2_inplace": (_I, [_P, _L, _I, _P]),
     "sllm_moe_route": (_I, [_P, _P, _L, _I, _I, _P]),
     "sllm_moe_route_grouped": (_I, [_P, _P, _L, _I, _I, _I, _I, _F, _F, _P]),
-    "sllm_moe_clamped_glu_scale": (_I, [_P, _P, _P, _L, _I, _I, _F, _I, _F, _F, _I, _P]),
+    "sllm_moe_clamped_glu_scale": (_I, [_P, _P, _P, _L, _I, _I, _F, _I, _F, _F, _I, _I, _P]),
     "sllm_moe_relu2_scale_inplace": (_I, [_P, _P, _L, _I, _I, _I, _P]),
     "sllm_latent_kv_store": (_I, [_P, _L, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _L, _I, _I, _I, _F, _I, _P]),
     "sllm_latent_attention_set_simt": (_I, [_I]),
     "sllm_latent_attention": (_I, [_P, _L, _L, _P, _L, _L, _P, _P, _P, _L, _P, _I, _I, _I, _P, _I, _P, _P, _P, _L, _L, _L, _I, _I,
                                    _I, _I, _I, _F, _I, _P, _I, _P]),
-    "sllm_window_kv_store": (_I, [_P, _L, _P, _L, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _L, _I, _I, _I, _I, _I, _F, _P, _P, _I, _P]),
+    "sllm_window_kv_store": (_I, [_P, _L, _P, _L, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _L, _I, _I, _I, _I, _I, _F, _P, _P, _P, _F,
+                                  _I, _I, _P]),
     "sllm_window_attention_set_simt": (_I, [_I]),
     "sllm_window_attention": (_I, [_P, _L, _P, _P, _P, _L, _P, _I, _I, _I, _P, _I, _P, _P, _P, _L, _L, _L, _I, _I, _I, _I, _I, _I,
-                                   _F, _I, _I, _F, _F, _P, _P, _F, _I, _P]),
+                                   _F, _I, _I, _F, _F, _P, _P, _F, _P, _F, _I, _I, _I, _I, _P]),
+    "sllm_diff_combine": (_I, [_P, _P, _L, _P, _L, _L, _I, _I, _I, _F, _F, _F, _I, _P]),
+    "sllm_group_norm_add_norm": (_I, [_P, _P, _P, _F, _P, _P, _F, _L, _I, _I, _I, _P]),
+    "sllm_group_norm_cast": (_I, [_P, _P, _P, _F, _L, _I, _I, _I, _P]),
+    "sllm_stream_add": (_I, [_P, _P, _P, _L, _I, _P]),
+    "sllm_gelu_glu": (_I, [_P, _P, _L, _I, _I, _P]),
+    "sllm_moe_route_softmax": (_I, [_P, _P, _L, _I, _I, _I, _P]),
+    "sllm_short_conv": (_I, [_P, _L, _I, _P, _P, _P, _P, _P, _P, _I, _L, _L, _I, _I, _I, _I, _P]),
+    "sllm_conv_tail_update": (_I, [_P, _L, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "sllm_mingru_scan": (_I, [_P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
+    "sllm_selective_scan": (_I, [_P, _L, _P, _L, _I, _P, _P, _P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "sllm_embed_pair_hash": (_I, [_P, _P, _P, _P, _P, _P, _I, _L, _L, _P, _P, _P, _L, _I, _I, _P]),
     "sllm_store_last_tokens": (_I, [_P, _P, _P, _P, _I, _P]),
     "sllm_postnorm_add_mix": (_I, [_P, _P, _P, _F, _P, _I, _P, _P, _L, _I, _I, _P]),

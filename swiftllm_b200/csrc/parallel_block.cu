@@ -73,7 +73,8 @@ __global__ void moe_relu2_scale_kernel(T* __restrict__ u, const float* __restric
 // so that ONE down projection over the concatenated experts yields the weighted sum of the chosen experts plus the shared one.
 template <typename T>
 __global__ void moe_clamped_glu_scale_kernel(const T* __restrict__ u, const float* __restrict__ w, T* __restrict__ y, int64_t n,
-                                             int experts, int ff, float limit, int sff, float shared_limit, float alpha) {
+                                             int experts, int ff, float limit, int sff, float shared_limit, float alpha,
+                                             int shared_gated) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int64_t cols = (int64_t)experts * ff + sff;
@@ -83,14 +84,14 @@ __global__ void moe_clamped_glu_scale_kernel(const T* __restrict__ u, const floa
     float wt, lim, g, v;
     if (c < (int64_t)experts * ff) {
         const int e = (int)(c / ff), f = (int)(c - (int64_t)e * ff);
-        wt = w[t * experts + e];
+        wt = w[t * (experts + shared_gated) + e];
         if (wt == 0.f) { stf(y + i, 0.f); return; }
         lim = limit;
         g = ldf(ur + (int64_t)e * 2 * ff + f);
         v = ldf(ur + (int64_t)e * 2 * ff + ff + f);
     } else {
         const int f = (int)(c - (int64_t)experts * ff);
-        wt = 1.f;
+        wt = shared_gated ? w[t * (experts + 1) + experts] : 1.f;      // a gated shared expert: the weights' extra last column
         lim = shared_limit;
         g = ldf(ur + (int64_t)experts * 2 * ff + f);
         v = ldf(ur + (int64_t)experts * 2 * ff + sff + f);
@@ -278,14 +279,16 @@ int sllm_moe_route_grouped(const void* logits, void* weights, int64_t num_tokens
 }
 
 int sllm_moe_clamped_glu_scale(const void* u, const void* weights, void* y, int64_t num_tokens, int experts, int ff, float limit,
-                               int shared_ff, float shared_limit, float alpha, sllm_dtype_t dtype, sllm_stream_t stream) {
+                               int shared_ff, float shared_limit, float alpha, int shared_gated, sllm_dtype_t dtype,
+                               sllm_stream_t stream) {
     SLLM_REQUIRE(num_tokens >= 0 && experts >= 0 && ff >= 0 && shared_ff >= 0 && (int64_t)experts * ff + shared_ff > 0,
                  "moe_clamped_glu_scale: bad shape");
     const int64_t n = num_tokens * ((int64_t)experts * ff + shared_ff);
     if (n == 0) return 0;
-    SLLM_REQUIRE(u && y && (weights || experts == 0), "moe_clamped_glu_scale: null pointer");
+    SLLM_REQUIRE(u && y && (weights || (experts == 0 && !shared_gated)), "moe_clamped_glu_scale: null pointer");
+    shared_gated = shared_gated ? 1 : 0;
     SLLM_DISPATCH_DTYPE_F32(dtype, (moe_clamped_glu_scale_kernel<T><<<(unsigned)cdiv(n, 256), 256, 0, (cudaStream_t)stream>>>(
-        (const T*)u, (const float*)weights, (T*)y, n, experts, ff, limit, shared_ff, shared_limit, alpha)));
+        (const T*)u, (const float*)weights, (T*)y, n, experts, ff, limit, shared_ff, shared_limit, alpha, shared_gated)));
     return check_launch("moe_clamped_glu_scale");
 }
 

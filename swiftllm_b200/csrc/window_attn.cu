@@ -15,23 +15,35 @@
 //   vcos / vsin        the value at position j is stored turned by j (pairs (m, m + dv/2) when `halves`, else (2m, 2m+1), angle
 //                      tables [T, dv/2]) and the head's output at position i is turned back by -i
 //   out_scale          factor on the output (a mixer that is summed with another one folds its weight here)
+//   pre-norm weights   queries / keys are RMS-normed over the head (x / sqrt(mean + prenorm_eps) * weight[dk]) BEFORE they turn
+//   chunk > 0          a query at position p sees only keys of its own chunk: positions >= floor(p / chunk) * chunk
+//   vshare > 1         `vshare` neighbouring key heads share ONE value head (value head = key head / vshare; the cache row holds
+//                      G keys and G / vshare values): several score maps over the same values, each its own query head
+//   out_f32            the output is written as fp32 whatever the storage type (a combine step follows)
+// diff_combine: per token and head, o = a1 - lambda * a2 of two maps' outputs, o / sqrt(mean(o^2) + eps) * factor * sigmoid(gate).
 #include "mma_helpers.cuh"
 #include "typed_io.cuh"
 
 namespace sllm {
 
 // entry j of a head row x turned by the token's angles (cs / sn: the token's table rows); entries from rot_dims on pass through
+// nw: weight of a norm over the head that comes BEFORE the turn (entry j is x[j] * inv * nw[j]), or null
+template <typename T>
+__device__ __forceinline__ float pre_entry(const T* __restrict__ x, int j, float inv, const float* __restrict__ nw) {
+    const float v = ldf(x + j);
+    return nw != nullptr ? v * inv * nw[j] : v;
+}
 template <typename T>
 __device__ __forceinline__ float rot_entry(const T* __restrict__ x, int j, int rot_dims, int halves, const float* __restrict__ cs,
-                                           const float* __restrict__ sn) {
-    if (j >= rot_dims) return ldf(x + j);
+                                           const float* __restrict__ sn, float inv = 1.f, const float* __restrict__ nw = nullptr) {
+    if (j >= rot_dims) return pre_entry(x, j, inv, nw);
     if (halves) {
         const int half = rot_dims >> 1;
-        if (j < half) return ldf(x + j) * cs[j] - ldf(x + j + half) * sn[j];
-        return ldf(x + j) * cs[j - half] + ldf(x + j - half) * sn[j - half];
+        if (j < half) return pre_entry(x, j, inv, nw) * cs[j] - pre_entry(x, j + half, inv, nw) * sn[j];
+        return pre_entry(x, j, inv, nw) * cs[j - half] + pre_entry(x, j - half, inv, nw) * sn[j - half];
     }
     const int i = j >> 1;
-    const float a = ldf(x + 2 * i), b = ldf(x + 2 * i + 1);
+    const float a = pre_entry(x, 2 * i, inv, nw), b = pre_entry(x, 2 * i + 1, inv, nw);
     return (j & 1) ? b * cs[i] + a * sn[i] : a * cs[i] - b * sn[i];
 }
 
@@ -44,11 +56,12 @@ __global__ void __launch_bounds__(128) window_kv_store_kernel(
     const float* __restrict__ sinb, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
     const int* __restrict__ block_table, int max_blocks_per_seq, T* __restrict__ cache, int n_slots, int slot, int block_size,
     int G, int dk, int dv, int rot_dims, int halves, float qk_norm_eps, const float* __restrict__ vcos,
-    const float* __restrict__ vsin) {
+    const float* __restrict__ vsin, const float* __restrict__ knorm_w, float prenorm_eps, int vshare) {
     const int64_t t = blockIdx.x;
     const int pos = tok_pos[t];
     const int blk = block_table[(int64_t)tok_seq[t] * max_blocks_per_seq + pos / block_size];
-    const int kw = G * dk, vw = G * dv;
+    const int GV = G / vshare;
+    const int kw = G * dk, vw = GV * dv;
     T* dst = cache + (((int64_t)blk * n_slots + slot) * block_size + pos % block_size) * (kw + vw);
     const T* kr = k + t * k_stride;
     const T* vr = v + t * v_stride;
@@ -57,13 +70,20 @@ __global__ void __launch_bounds__(128) window_kv_store_kernel(
     const float* sn = sinb != nullptr ? sinb + t * (rot_dims >> 1) : nullptr;
     for (int g = warp; g < G; g += nwarps) {
         const T* x = kr + g * dk;
+        float pinv = 1.f;
+        if (knorm_w != nullptr) {
+            float ss = 0.f;
+            for (int j = lane; j < dk; j += 32) { const float o = ldf(x + j); ss += o * o; }
+            pinv = 1.f / sqrtf(warp_sum(ss) / (float)dk + prenorm_eps);
+        }
         float inv = 1.f;
         if (qk_norm_eps >= 0.f) {
             float ss = 0.f;
-            for (int j = lane; j < dk; j += 32) { const float o = rot_entry(x, j, rot_dims, halves, cs, sn); ss += o * o; }
+            for (int j = lane; j < dk; j += 32) { const float o = rot_entry(x, j, rot_dims, halves, cs, sn, pinv, knorm_w); ss += o * o; }
             inv = 1.f / sqrtf(warp_sum(ss) / (float)dk + qk_norm_eps);
         }
-        for (int j = lane; j < dk; j += 32) stf(dst + g * dk + j, rot_entry(x, j, rot_dims, halves, cs, sn) * inv);
+        for (int j = lane; j < dk; j += 32) stf(dst + g * dk + j, rot_entry(x, j, rot_dims, halves, cs, sn, pinv, knorm_w) * inv);
+        if (g >= GV) continue;                          // value heads: the first G / vshare turns of this loop
         const T* y = vr + g * dv;
         if (vcos != nullptr) {
             const float* vc = vcos + t * (dv >> 1);
@@ -89,7 +109,8 @@ __global__ void __launch_bounds__(WA_MAX_HPB * 32) window_attn_kernel(
     const int* __restrict__ block_table, int max_blocks_per_seq, const int* __restrict__ tok_seq,
     const int* __restrict__ tok_pos, T* __restrict__ out, int64_t out_stride_t,  // [T, H, dv]
     int H, int G, int dk, int dv, int rot_dims, int window, float scale, float sink, int halves, float qk_norm_eps,
-    float softcap, const float* __restrict__ vcos, const float* __restrict__ vsin, float out_scale) {
+    float softcap, const float* __restrict__ vcos, const float* __restrict__ vsin, float out_scale,
+    const float* __restrict__ qnorm_w, float prenorm_eps, int chunk, int vshare, int out_f32) {
     extern __shared__ float smem[];
     const int KP = dk + 1;
     const int hpb = blockDim.x >> 5;
@@ -103,16 +124,22 @@ __global__ void __launch_bounds__(WA_MAX_HPB * 32) window_attn_kernel(
     const int g = (blockIdx.y * hpb) / (H / G);
     const int pos = tok_pos[t];
     const int* bt = block_table + (int64_t)tok_seq[t] * max_blocks_per_seq;
-    const int row = G * (dk + dv);
+    const int row = G * dk + (G / vshare) * dv;
 
     {
         float* qw = qs + warp * dk;
         const T* qr = q + t * q_stride_t + (int64_t)h * dk;
         const float* cs = cosb != nullptr ? cosb + t * (rot_dims >> 1) : nullptr;
         const float* sn = sinb != nullptr ? sinb + t * (rot_dims >> 1) : nullptr;
+        float pinv = 1.f;
+        if (qnorm_w != nullptr) {
+            float s0 = 0.f;
+            for (int j = lane; j < dk; j += 32) { const float o = ldf(qr + j); s0 += o * o; }
+            pinv = 1.f / sqrtf(warp_sum(s0) / (float)dk + prenorm_eps);
+        }
         float ss = 0.f;
         for (int j = lane; j < dk; j += 32) {
-            const float o = rot_entry(qr, j, rot_dims, halves, cs, sn);
+            const float o = rot_entry(qr, j, rot_dims, halves, cs, sn, pinv, qnorm_w);
             qw[j] = o;
             ss += o * o;
         }
@@ -126,7 +153,8 @@ __global__ void __launch_bounds__(WA_MAX_HPB * 32) window_attn_kernel(
 #pragma unroll
     for (int k = 0; k < KR; k++) acc[k] = 0.f;
 
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (chunk > 0) lo = max(lo, pos / chunk * chunk);
     for (int base = lo; base <= pos; base += WA_TILE) {
         __syncthreads();                       // the previous tile is no longer read (and qs is written, first time round)
         const int nkeys = min(WA_TILE, pos - base + 1);
@@ -134,7 +162,7 @@ __global__ void __launch_bounds__(WA_MAX_HPB * 32) window_attn_kernel(
             const int kp = base + jj;
             const T* src = cache + (((int64_t)bt[kp / block_size] * n_slots + slot) * block_size + kp % block_size) * row;
             const T* ks = src + g * dk;
-            const T* vs = src + G * dk + g * dv;
+            const T* vs = src + G * dk + (g / vshare) * dv;
             for (int d = lane; d < dk; d += 32) kt[jj * KP + d] = ldf(ks + d);
             for (int d = lane; d < dv; d += 32) vt[jj * dv + d] = ldf(vs + d);
         }
@@ -197,7 +225,8 @@ __global__ void __launch_bounds__(WA_MAX_HPB * 32) window_attn_kernel(
         if (d < dv) {
             float y = acc[k] / denom * out_scale;
             if (gr != nullptr) y *= 1.f / (1.f + expf(-ldf(gr + d)));
-            stf(o + d, y);
+            if (out_f32) reinterpret_cast<float*>(out)[t * out_stride_t + (int64_t)h * dv + d] = y;
+            else stf(o + d, y);
         }
     }
 }
@@ -223,7 +252,8 @@ __global__ void __launch_bounds__(128, WT_KEYS == 32 ? 3 : 2) window_attn_mma_ke
     const int* __restrict__ block_table, int max_blocks_per_seq, const int* __restrict__ tok_seq,
     const int* __restrict__ tok_pos, T* __restrict__ out, int64_t out_stride_t, int row0, int nrows, int qt, int hq, int hqp_log2,
     int H, int G, int dk, int dv, int rot_dims, int window, float scale_log2, float sink, int halves, float qk_norm_eps,
-    float softcap, const float* __restrict__ vcos, const float* __restrict__ vsin, float out_scale) {
+    float softcap, const float* __restrict__ vcos, const float* __restrict__ vsin, float out_scale,
+    const float* __restrict__ qnorm_w, float prenorm_eps, int chunk, int vshare, int out_f32) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int PQ = dk * 2 + 16, PK = dk * 2 + 16, PV = dv * 2 + 16;            // row pitches in bytes
     unsigned char* Qs = smem_raw;                                              // [64][PQ]
@@ -234,7 +264,7 @@ __global__ void __launch_bounds__(128, WT_KEYS == 32 ? 3 : 2) window_attn_mma_ke
     const int hqp = 1 << hqp_log2;
     const int t_first = row0 + blockIdx.x * qt;
     const int ntok = min(qt, row0 + nrows - t_first);
-    const int row_elems = G * (dk + dv);
+    const int row_elems = G * dk + (G / vshare) * dv;
     const int ck = dk >> 3, cv = dv >> 3;                                      // 16-byte chunks per key / value row
     const int half = rot_dims >> 1;
     // with a score cap: cap * tanh(s * scale / cap), then to base 2
@@ -248,7 +278,8 @@ __global__ void __launch_bounds__(128, WT_KEYS == 32 ? 3 : 2) window_attn_mma_ke
         int n = 1;
         while (i0 + n < ntok && tok_seq[ts + n] == seq && tok_pos[ts + n] == pos0 + n) n++;
         const int* bt = block_table + (int64_t)seq * max_blocks_per_seq;
-        const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+        int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+        if (chunk > 0) lo = max(lo, pos0 / chunk * chunk);
         const int hi = pos0 + n - 1;
         const int ntiles = (hi - lo) / WT_KEYS + 1;
         __syncthreads();                                                       // the previous segment's tiles and queries are done with
@@ -265,7 +296,7 @@ __global__ void __launch_bounds__(128, WT_KEYS == 32 ? 3 : 2) window_attn_mma_ke
                 const int b = kp / block_size;
                 const int64_t rowi = ((int64_t)bt[b] * n_slots + slot) * block_size + (kp - b * block_size);
                 krow = cache + rowi * row_elems + g * dk;
-                vrow = cache + rowi * row_elems + G * dk + g * dv;
+                vrow = cache + rowi * row_elems + G * dk + (g / vshare) * dv;
             }
             const int nb = ok ? 16 : 0;
             const uint32_t kd = smem_u32(Ks + (st * WT_KEYS + jj) * PK), vd = smem_u32(Vs + (st * WT_KEYS + jj) * PV);
@@ -285,12 +316,24 @@ __global__ void __launch_bounds__(128, WT_KEYS == 32 ? 3 : 2) window_attn_mma_ke
             const T* qr = q + t * q_stride_t + (int64_t)(g * hq + hh) * dk;
             const float* cs = cosb != nullptr ? cosb + t * half : nullptr;
             const float* sn = sinb != nullptr ? sinb + t * half : nullptr;
+            float pinv = 1.f;
+            if (qnorm_w != nullptr) {
+                float s0 = 0.f;
+                if (live)
+                    for (int i = tid & 1; i < (dk >> 1); i += 2) {
+                        const float a = ldf(qr + 2 * i), b = ldf(qr + 2 * i + 1);
+                        s0 += a * a + b * b;
+                    }
+                s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
+                pinv = 1.f / sqrtf(s0 / (float)dk + prenorm_eps);
+            }
             float inv = 1.f;
             if (qk_norm_eps >= 0.f) {
                 float ss = 0.f;
                 if (live)
                     for (int i = tid & 1; i < (dk >> 1); i += 2) {
-                        const float a = rot_entry(qr, 2 * i, rot_dims, halves, cs, sn), b = rot_entry(qr, 2 * i + 1, rot_dims, halves, cs, sn);
+                        const float a = rot_entry(qr, 2 * i, rot_dims, halves, cs, sn, pinv, qnorm_w),
+                                    b = rot_entry(qr, 2 * i + 1, rot_dims, halves, cs, sn, pinv, qnorm_w);
                         ss += a * a + b * b;
                     }
                 ss += __shfl_xor_sync(0xffffffffu, ss, 1);
@@ -299,8 +342,8 @@ __global__ void __launch_bounds__(128, WT_KEYS == 32 ? 3 : 2) window_attn_mma_ke
             for (int i = tid & 1; i < (dk >> 1); i += 2) {
                 float a = 0.f, b = 0.f;
                 if (live) {
-                    a = rot_entry(qr, 2 * i, rot_dims, halves, cs, sn) * inv;
-                    b = rot_entry(qr, 2 * i + 1, rot_dims, halves, cs, sn) * inv;
+                    a = rot_entry(qr, 2 * i, rot_dims, halves, cs, sn, pinv, qnorm_w) * inv;
+                    b = rot_entry(qr, 2 * i + 1, rot_dims, halves, cs, sn, pinv, qnorm_w) * inv;
                 }
                 *reinterpret_cast<uint32_t*>(Qs + r * PQ + i * 4) = pack2<T>(a, b);
             }
@@ -311,11 +354,14 @@ __global__ void __launch_bounds__(128, WT_KEYS == 32 ? 3 : 2) window_attn_mma_ke
         const int j_a = r_a >> hqp_log2, j_b = r_b >> hqp_log2;
         const bool live_a = j_a < n && (r_a & (hqp - 1)) < hq, live_b = j_b < n && (r_b & (hqp - 1)) < hq;
         const int pos_a = pos0 + j_a, pos_b = pos0 + j_b;
-        const int lo_a = window > 0 ? pos_a - window + 1 : 0, lo_b = window > 0 ? pos_b - window + 1 : 0;
+        int lo_a = window > 0 ? pos_a - window + 1 : 0, lo_b = window > 0 ? pos_b - window + 1 : 0;
+        if (chunk > 0) { lo_a = max(lo_a, pos_a / chunk * chunk); lo_b = max(lo_b, pos_b / chunk * chunk); }
         // keys any row of this warp can see (warp-uniform): tiles outside are skipped
         const int wj_min = (warp * 16) >> hqp_log2, wj_max = min((warp * 16 + 15) >> hqp_log2, n - 1);
         const bool warp_live = wj_min < n;
-        const int w_lo = window > 0 ? max(0, pos0 + wj_min - window + 1) : 0, w_hi = pos0 + wj_max;
+        int w_lo = window > 0 ? max(0, pos0 + wj_min - window + 1) : 0;
+        if (chunk > 0) w_lo = max(w_lo, (pos0 + wj_min) / chunk * chunk);
+        const int w_hi = pos0 + wj_max;
         float m_a = sink > 0.f ? 0.f : -INFINITY, m_b = m_a;
         float l_a = (lane & 3) == 0 ? sink : 0.f, l_b = l_a;
         float o[DMAX / 8][4];
@@ -458,11 +504,53 @@ __global__ void __launch_bounds__(128, WT_KEYS == 32 ? 3 : 2) window_attn_mma_ke
                         y0 *= 1.f / (1.f + __expf(-ldf(grow + d)));
                         y1 *= 1.f / (1.f + __expf(-ldf(grow + d + 1)));
                     }
-                    *reinterpret_cast<uint32_t*>(orow + d) = pack2<T>(y0, y1);
+                    if (out_f32) {
+                        float* o32 = reinterpret_cast<float*>(out) + t * out_stride_t + (int64_t)h * dv + d;
+                        o32[0] = y0; o32[1] = y1;
+                    } else {
+                        *reinterpret_cast<uint32_t*>(orow + d) = pack2<T>(y0, y1);
+                    }
                 }
             }
         }
         i0 += n;
+    }
+}
+
+// ------------------------------------------------------------------ two maps -> one head
+// a: fp32 [T, G, 2, hq, dv] (the attention above with vshare = 2 and queries ordered [key/value head][map][head of the group]).
+// One warp per (token, head h = g hq + hh): o = a[g, 0, hh] - lambda a[g, 1, hh]; out = o / sqrt(mean(o^2) + eps) * factor *
+// sigmoid(gate[t, h]) in the storage type, heads in their natural order.  KR: registers per lane, dv <= 32 KR.
+template <typename T, int KR>
+__global__ void __launch_bounds__(256) diff_combine_kernel(const float* __restrict__ a, const T* __restrict__ gate,
+                                                           int64_t gate_stride_t, T* __restrict__ out, int64_t out_stride_t,
+                                                           int64_t units, int H, int hq, int dv, float lambda, float eps,
+                                                           float factor) {
+    const int lane = threadIdx.x & 31;
+    const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= units) return;
+    const int64_t t = unit / H;
+    const int h = (int)(unit - t * H), g = h / hq, hh = h - g * hq;
+    const float* a1 = a + (t * 2 * H + (int64_t)(g * 2 * hq + hh)) * dv;
+    const float* a2 = a1 + (int64_t)hq * dv;
+    float o[KR], ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < KR; k++) {
+        const int d = lane + 32 * k;
+        o[k] = d < dv ? a1[d] - lambda * a2[d] : 0.f;
+        ss += o[k] * o[k];
+    }
+    const float f = factor / sqrtf(warp_sum(ss) / (float)dv + eps);
+    const T* gr = gate != nullptr ? gate + t * gate_stride_t + (int64_t)h * dv : nullptr;
+    T* orow = out + t * out_stride_t + (int64_t)h * dv;
+#pragma unroll
+    for (int k = 0; k < KR; k++) {
+        const int d = lane + 32 * k;
+        if (d < dv) {
+            float y = o[k] * f;
+            if (gr != nullptr) y *= 1.f / (1.f + expf(-ldf(gr + d)));
+            stf(orow + d, y);
+        }
     }
 }
 
@@ -475,7 +563,8 @@ static int launch_window_attn_mma(const void* q, int64_t q_stride_t, const void*
                                   const void* block_table, int max_blocks_per_seq, const void* tok_seq, const void* tok_pos,
                                   void* out, int64_t out_stride_t, int64_t num_tokens, int64_t num_prefill, int H, int G, int dk,
                                   int dv, int rot_dims, int window, float scale, float sink, int halves, float qk_norm_eps,
-                                  float softcap, const void* vcos, const void* vsin, float out_scale, cudaStream_t stream) {
+                                  float softcap, const void* vcos, const void* vsin, float out_scale, const void* qnorm_w,
+                                  float prenorm_eps, int chunk, int vshare, int out_f32, cudaStream_t stream) {
     static unsigned long long attr_mask = 0;
     const int hq = H / G;
     int hqp_log2 = 0;
@@ -503,7 +592,8 @@ static int launch_window_attn_mma(const void* q, int64_t q_stride_t, const void*
             (const T*)q, q_stride_t, (const float*)cosb, (const float*)sinb, (const T*)gate, gate_stride_t, (const T*)cache,
             n_slots, slot, block_size, (const int*)block_table, max_blocks_per_seq, (const int*)tok_seq, (const int*)tok_pos,
             (T*)out, out_stride_t, (int)first, (int)count, qt, hq, hqp_log2, H, G, dk, dv, rot_dims, window, scale_log2, sink,
-            halves, qk_norm_eps, softcap, (const float*)vcos, (const float*)vsin, out_scale);
+            halves, qk_norm_eps, softcap, (const float*)vcos, (const float*)vsin, out_scale, (const float*)qnorm_w, prenorm_eps,
+            chunk, vshare, out_f32);
     }
     return check_launch("window_attention (tensor cores)");
 }
@@ -520,7 +610,8 @@ static int launch_window_attn(const void* q, int64_t q_stride_t, const void* cos
                               const void* block_table, int max_blocks_per_seq, const void* tok_seq, const void* tok_pos, void* out,
                               int64_t out_stride_t, int64_t num_tokens, int H, int G, int dk, int dv, int rot_dims, int window,
                               float scale, float sink, int halves, float qk_norm_eps, float softcap, const void* vcos,
-                              const void* vsin, float out_scale, cudaStream_t stream) {
+                              const void* vsin, float out_scale, const void* qnorm_w, float prenorm_eps, int chunk, int vshare,
+                              int out_f32, cudaStream_t stream) {
     static unsigned long long attr_mask = 0;
     const int hpb = heads_per_cta(H / G);
     const size_t smem = ((size_t)hpb * dk + (size_t)WA_TILE * (dk + 1) + (size_t)WA_TILE * dv + (size_t)hpb * dv) * sizeof(float);
@@ -532,7 +623,7 @@ static int launch_window_attn(const void* q, int64_t q_stride_t, const void* cos
         (const T*)q, q_stride_t, (const float*)cosb, (const float*)sinb, (const T*)gate, gate_stride_t, (const T*)cache, n_slots,
         slot, block_size, (const int*)block_table, max_blocks_per_seq, (const int*)tok_seq, (const int*)tok_pos, (T*)out,
         out_stride_t, H, G, dk, dv, rot_dims, window, scale, sink, halves, qk_norm_eps, softcap, (const float*)vcos,
-        (const float*)vsin, out_scale);
+        (const float*)vsin, out_scale, (const float*)qnorm_w, prenorm_eps, chunk, vshare, out_f32);
     return check_launch("window_attention");
 }
 
@@ -546,7 +637,10 @@ int sllm_window_kv_store(const void* k, int64_t k_row_stride, const void* v, int
                          const void* sinb, const void* tok_seq, const void* tok_pos, const void* block_table,
                          int max_blocks_per_seq, void* cache, int n_slots, int slot, int block_size, int64_t num_tokens,
                          int num_kv_heads, int dk, int dv, int rot_dims, int pair_halves, float qk_norm_eps, const void* vcos,
-                         const void* vsin, sllm_dtype_t dtype, sllm_stream_t stream) {
+                         const void* vsin, const void* knorm_w, float prenorm_eps, int vshare, sllm_dtype_t dtype,
+                         sllm_stream_t stream) {
+    SLLM_REQUIRE(vshare >= 1 && num_kv_heads % vshare == 0, "window_kv_store: %d key heads cannot share values in runs of %d",
+                 num_kv_heads, vshare);
     SLLM_REQUIRE(num_tokens >= 0 && num_kv_heads > 0 && dk > 0 && dv > 0 && rot_dims >= 0 && rot_dims <= dk && rot_dims % 2 == 0,
                  "window_kv_store: bad shape (kv heads %d, dk %d, dv %d, rot_dims %d)", num_kv_heads, dk, dv, rot_dims);
     SLLM_REQUIRE((vcos == nullptr) == (vsin == nullptr) && (vcos == nullptr || dv % 2 == 0),
@@ -558,7 +652,8 @@ int sllm_window_kv_store(const void* k, int64_t k_row_stride, const void* v, int
     SLLM_DISPATCH_DTYPE_F32(dtype, (window_kv_store_kernel<T><<<(unsigned)num_tokens, 128, 0, (cudaStream_t)stream>>>(
         (const T*)k, k_row_stride, (const T*)v, v_row_stride, (const float*)cosb, (const float*)sinb, (const int*)tok_seq,
         (const int*)tok_pos, (const int*)block_table, max_blocks_per_seq, (T*)cache, n_slots, slot, block_size, num_kv_heads,
-        dk, dv, rot_dims, pair_halves, qk_norm_eps, (const float*)vcos, (const float*)vsin)));
+        dk, dv, rot_dims, pair_halves, qk_norm_eps, (const float*)vcos, (const float*)vsin, (const float*)knorm_w, prenorm_eps,
+        vshare)));
     return check_launch("window_kv_store");
 }
 
@@ -573,8 +668,11 @@ int sllm_window_attention(const void* q, int64_t q_stride_t, const void* cosb, c
                           const void* block_table, int max_blocks_per_seq, const void* tok_seq, const void* tok_pos, void* out,
                           int64_t out_stride_t, int64_t num_tokens, int64_t num_prefill_tokens, int num_heads, int num_kv_heads,
                           int dk, int dv, int rot_dims, int window, float scale, int sink, int pair_halves, float qk_norm_eps,
-                          float softcap, const void* vcos, const void* vsin, float out_scale, sllm_dtype_t dtype,
-                          sllm_stream_t stream) {
+                          float softcap, const void* vcos, const void* vsin, float out_scale, const void* qnorm_w,
+                          float prenorm_eps, int chunk, int vshare, int out_f32, sllm_dtype_t dtype, sllm_stream_t stream) {
+    SLLM_REQUIRE(vshare >= 1 && num_kv_heads % vshare == 0 && chunk >= 0 && (!out_f32 || vcos == nullptr),
+                 "window_attention: %d key heads in runs of %d; chunk %d >= 0; fp32 output excludes turned values", num_kv_heads,
+                 vshare, chunk);
     SLLM_REQUIRE((vcos == nullptr) == (vsin == nullptr) && (vcos == nullptr || dv % 2 == 0) && softcap >= 0.f,
                  "window_attention: turned values need both angle tables and an even value size (dv %d); softcap >= 0", dv);
     SLLM_REQUIRE(num_tokens >= 0 && num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0 && dk > 0 && dv > 0 &&
@@ -594,7 +692,7 @@ int sllm_window_attention(const void* q, int64_t q_stride_t, const void* cosb, c
     SLLM_DISPATCH_DTYPE(dtype, return (launch_window_attn_mma<T, DMAX>(q, q_stride_t, cosb, sinb, gate, gate_stride_t, cache,  \
         n_slots, slot, block_size, block_table, max_blocks_per_seq, tok_seq, tok_pos, out, out_stride_t, num_tokens,         \
         num_prefill_tokens, num_heads, num_kv_heads, dk, dv, rot_dims, window, scale, sinkw, pair_halves, qk_norm_eps, softcap, \
-        vcos, vsin, out_scale, (cudaStream_t)stream)))
+        vcos, vsin, out_scale, qnorm_w, prenorm_eps, chunk, vshare, out_f32, (cudaStream_t)stream)))
         if (dk <= 64 && dv <= 64) { WA_MMA(64); }
         else { WA_MMA(128); }
 #undef WA_MMA
@@ -603,13 +701,33 @@ int sllm_window_attention(const void* q, int64_t q_stride_t, const void* cosb, c
     SLLM_DISPATCH_DTYPE_F32(dtype, return (launch_window_attn<T, KR>(q, q_stride_t, cosb, sinb, gate, gate_stride_t, cache,   \
         n_slots, slot, block_size, block_table, max_blocks_per_seq, tok_seq, tok_pos, out, out_stride_t, num_tokens,        \
         num_heads, num_kv_heads, dk, dv, rot_dims, window, scale, sinkw, pair_halves, qk_norm_eps, softcap, vcos, vsin,      \
-        out_scale, (cudaStream_t)stream)))
+        out_scale, qnorm_w, prenorm_eps, chunk, vshare, out_f32, (cudaStream_t)stream)))
     if (dv <= 32) { WA_LAUNCH(1); }
     else if (dv <= 64) { WA_LAUNCH(2); }
     else if (dv <= 128) { WA_LAUNCH(4); }
     else { WA_LAUNCH(8); }
 #undef WA_LAUNCH
     return 0;
+}
+
+int sllm_diff_combine(const void* a, const void* gate, int64_t gate_stride_t, void* out, int64_t out_stride_t, int64_t num_tokens,
+                      int num_heads, int num_kv_heads, int dv, float lambda, float eps, float factor, sllm_dtype_t dtype,
+                      sllm_stream_t stream) {
+    SLLM_REQUIRE(num_tokens >= 0 && num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0 && dv > 0 && dv <= 256,
+                 "diff_combine: bad shape (heads %d / %d, dv %d <= 256)", num_heads, num_kv_heads, dv);
+    if (num_tokens == 0) return 0;
+    SLLM_REQUIRE(a && out, "diff_combine: null pointer");
+    const int64_t units = num_tokens * num_heads;
+    const int hq = num_heads / num_kv_heads;
+#define DC_LAUNCH(KR)                                                                                                       \
+    SLLM_DISPATCH_DTYPE_F32(dtype, (diff_combine_kernel<T, KR><<<(unsigned)cdiv(units, 8), 256, 0, (cudaStream_t)stream>>>(   \
+        (const float*)a, (const T*)gate, gate_stride_t, (T*)out, out_stride_t, units, num_heads, hq, dv, lambda, eps, factor)))
+    if (dv <= 32) { DC_LAUNCH(1); }
+    else if (dv <= 64) { DC_LAUNCH(2); }
+    else if (dv <= 128) { DC_LAUNCH(4); }
+    else { DC_LAUNCH(8); }
+#undef DC_LAUNCH
+    return check_launch("diff_combine");
 }
 
 }  // extern "C"

@@ -109,10 +109,18 @@ class WindowAttentionSpec:
     softcap: float = 0.0            # > 0: score <- softcap * tanh(score / softcap)
     value_rotation: bool = False    # values are turned by their position over all vdim entries (plain frequencies of rot_base)
     out_scale: float = 1.0          # factor on the mixer's output (its weight in a sum of mixers)
+    chunk: int = 0                  # > 0: a query at position p sees only positions >= floor(p / chunk) * chunk (and <= p)
+    # score maps per head: every query head and key head has `maps` parts of `dim` entries, each part an attention of its own
+    # over the head's values.  maps = 2 is differential attention: out = rms(map0 - lambda * map1) * (1 - diff), with
+    # lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff from four learned vectors
+    maps: int = 1
+    diff: float = 0.0
+    qk_weight_norm: bool = False    # RMS norm with a weight vector of `dim` entries on every query / key part BEFORE rotation
+    bias: bool = False              # q, k, v and the output projection have biases
 
     @property
     def cache_width(self) -> int:
-        return self.kv_heads * (self.dim + self.vdim)
+        return self.kv_heads * (self.maps * self.dim + self.vdim)
 
     @property
     def rot_key(self):
@@ -165,23 +173,50 @@ class GatedRecurrenceSpec:
 
 
 @dataclasses.dataclass(frozen=True)
+class MinGruSpec:
+    """A gated recurrence whose gates read only the current token: z = sigmoid(W_z h + b), candidate c = g(W_x h + b) with
+    g(u) = u + 1/2 for u >= 0 and sigmoid(u) below; S <- (1 - z) S + z c per channel (fp32, one per sequence); output
+    W_o (S * silu(W_g h)).  No cache rows."""
+    width: int
+    kv_from: Optional[int] = None
+    cache_width: int = 0
+
+
+@dataclasses.dataclass(frozen=True)
+class SelectiveScanSpec:
+    """A selective state-space mixer: W_in h = [x | z] (`inner` channels each); x through a causal convolution of `conv` taps and a
+    SiLU; W_x x = [dt (dt_rank) | B (state) | C (state)]; dt = softplus(W_dt dt + b); S[c, n] <- exp(dt_c A[c, n]) S + dt_c x_c B_n;
+    y_c = sum_n S[c, n] C_n + D_c x_c; output W_o (y * silu(z)).  No cache rows: S (fp32 [inner, state]) and the convolution's last
+    conv - 1 inputs live per sequence."""
+    inner: int
+    state: int
+    dt_rank: int
+    conv: int
+    kv_from: Optional[int] = None
+    cache_width: int = 0
+
+
+@dataclasses.dataclass(frozen=True)
 class FeedForwardSpec:
     kind: str                   # "dense" | "moe"
     ff: int                     # hidden size of the dense layer / of ONE expert
     experts: int = 0
     top: int = 0
     # "relu2": relu(up)^2 | "clamped_glu": min(gate, limit) * sigmoid(1.702 .) * (clamp(up) + 1) | "silu_glu": silu(gate) * up
+    # | "gelu_glu": gelu_tanh(gate) * up
     activation: str = "relu2"
     limit: float = 0.0          # clamped_glu: bound of the gate (above) and of the up projection (both sides)
     # routing.  "top_softmax": softmax over the `top` largest logits.  "softmax_grouped": scores are a softmax over all experts,
     # only experts of the `keep` best of `groups` groups can be chosen, the chosen scores are renormalised and scaled.
     # "sigmoid_bias": scores are sigmoids; the `top` largest score + bias (tensor `correction`) are chosen; weights are the scores.
+    # "softmax_top": scores are a softmax over all experts; the `top` largest are chosen; weights are those scores as they are.
     routing: str = "top_softmax"
     groups: int = 1
     keep: int = 1
     route_scale: float = 1.0
     shared_ff: int = 0          # hidden size of a shared expert that every token uses (0: none)
     shared_limit: float = 0.0
+    shared_gated: bool = False  # the shared expert's output is multiplied by sigmoid(w . h), one number per token
 
 
 def _cache_geometry(mixers):
@@ -398,3 +433,99 @@ class BuzaraxModelConfig:
     def load_from_model_path(model_path: str) -> "BuzaraxModelConfig":
         with open(os.path.join(model_path, "config.json"), "r", encoding="utf-8") as f:
             return BuzaraxModelConfig(json.load(f))
+
+
+# ---------------------------------------------------------------- Naforax
+class NaforaxModelConfig:
+    """config.json of the Naforax design: {"architecture": "Naforax", "vocab", "width", "norm": {"eps", "groups"}, "residual_mult",
+    "logit_softcap", "canon": {"taps"}, "loop": {"start", "stop", "times"} | absent, "layers": [{"type": "attention" | "mingru" |
+    "mamba1", "mixer": {...}, "mlp": {"kind": "dense", "ff"} | {"kind": "moe", "router": {"experts", "top"}, "expert": {"ff",
+    "limit"}, "shared": {"ff", "limit"} | absent} | null}, ...]}.
+    "attention": {"heads", "kv_heads", "dim", "vdim", "scale", "diff", "mask": {"size"}, "rot": {"base", "dims"}};
+    "mingru": {"width"}; "mamba1": {"inner", "state", "dt_rank", "conv"}.
+    Layers are sandwich blocks, x <- x + m * norm_b(sublayer(c(norm_a(x)))): group RMS norms before and after every sublayer, and
+    c(h) = h + causal per-channel convolution of h.  Layers start .. stop - 1 run `times` times in a row with the same weights;
+    `runs` lists (layer, pass) in running order; every run owns its cache rows and recurrent state.  Every size may differ from
+    layer to layer."""
+    family = "naforax"
+
+    def __init__(self, model_config: dict):
+        assert model_config.get("architecture") == "Naforax", f"not a Naforax config: {model_config.get('architecture')!r}"
+        self.raw = dict(model_config)
+        self.vocab_size = int(model_config["vocab"])
+        self.hidden_size = int(model_config["width"])
+        self.rms_norm_eps = float(model_config["norm"]["eps"])
+        self.norm_groups = int(model_config["norm"].get("groups", 1))
+        assert self.hidden_size % self.norm_groups == 0, "norm.groups must divide the width"
+        self.residual_mult = float(model_config.get("residual_mult", 1.0))
+        self.logit_softcap = float(model_config.get("logit_softcap") or 0.0)
+        self.canon_taps = int((model_config.get("canon") or {}).get("taps", 1))
+        assert 1 <= self.canon_taps <= 8, "1 <= canon.taps <= 8"
+        self.mixers, self.ffs = [], []
+        for i, layer in enumerate(model_config["layers"]):
+            m = layer["mixer"]
+            if layer["type"] == "attention":
+                rot = m.get("rot") or {}
+                mask = m.get("mask") or {}
+                spec = WindowAttentionSpec(
+                    heads=int(m["heads"]), kv_heads=int(m.get("kv_heads") or m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                    window=0, rot_base=float(rot.get("base", 10000.0)), rot_dims=int(rot.get("dims", 0)), scale=float(m["scale"]),
+                    sink=False, gate=True, chunk=int(mask.get("size", 0)), maps=2, diff=float(m["diff"]), qk_weight_norm=True,
+                    bias=True)
+                assert spec.heads % spec.kv_heads == 0, f"layer {i}: heads must be a multiple of kv_heads"
+                assert spec.rot_dims % 2 == 0 and spec.rot_dims <= spec.dim, f"layer {i}: rot.dims must be even and <= dim"
+            elif layer["type"] == "mingru":
+                spec = MinGruSpec(width=int(m["width"]))
+            else:
+                assert layer["type"] == "mamba1", f"layer {i}: unknown mixer type {layer['type']!r}"
+                spec = SelectiveScanSpec(inner=int(m["inner"]), state=int(m["state"]), dt_rank=int(m["dt_rank"]), conv=int(m["conv"]))
+                assert 1 <= spec.conv <= 8 and 1 <= spec.state <= 256, f"layer {i}: 1 <= conv <= 8, 1 <= state <= 256"
+            self.mixers.append(spec)
+            f = layer.get("mlp")
+            if f is None:
+                self.ffs.append(None)
+            elif f["kind"] == "dense":
+                self.ffs.append(FeedForwardSpec("dense", int(f["ff"]), activation="gelu_glu"))
+            else:
+                assert f["kind"] == "moe", f"layer {i}: unknown mlp kind {f['kind']!r}"
+                r, e, sh = f["router"], f["expert"], f.get("shared")
+                ff = FeedForwardSpec("moe", int(e["ff"]), int(r["experts"]), int(r["top"]), activation="clamped_glu",
+                                     limit=float(e["limit"]), routing="softmax_top", shared_ff=int(sh["ff"]) if sh else 0,
+                                     shared_limit=float(sh["limit"]) if sh else 0.0, shared_gated=bool(sh))
+                assert 0 < ff.top <= ff.experts, f"layer {i}: top must be in 1 .. experts"
+                self.ffs.append(ff)
+        self.num_layers = len(self.mixers)
+        loop = model_config.get("loop")
+        if loop:
+            a, b, times = int(loop["start"]), int(loop["stop"]), int(loop["times"])
+            assert 0 <= a < b <= self.num_layers and times >= 1, "loop: 0 <= start < stop <= layers, times >= 1"
+            self.loop = (a, b, times)
+            self.runs = [(i, 0) for i in range(a)] + [(i, t) for t in range(times) for i in range(a, b)] + \
+                [(i, 0) for i in range(b, self.num_layers)]
+        else:
+            self.loop = None
+            self.runs = [(i, 0) for i in range(self.num_layers)]
+        # cache rows and state are per RUN (a repeated layer keeps one set per pass)
+        self.cache_slot, self.cache_slots_per_width = _cache_geometry([self.mixers[i] for i, _ in self.runs])
+
+    def get_kvslot_size(self, dtype: torch.dtype = torch.bfloat16) -> int:
+        """Bytes of cache one token occupies: one [keys of both maps | values] row per attention run."""
+        return sum(w * n for w, n in self.cache_slots_per_width.items()) * dtype.itemsize
+
+    def get_state_size(self, dtype: torch.dtype = torch.bfloat16) -> int:
+        """Bytes of recurrent state one SEQUENCE occupies, whatever its length: the input convolutions' last inputs of both
+        sublayers (fp32) of every run, and the mixers' states."""
+        n = 0
+        for i, _ in self.runs:
+            s = self.mixers[i]
+            n += 4 * (self.canon_taps - 1) * self.hidden_size * (1 if self.ffs[i] is None else 2)
+            if isinstance(s, MinGruSpec):
+                n += 4 * s.width
+            elif isinstance(s, SelectiveScanSpec):
+                n += 4 * s.inner * s.state + (s.conv - 1) * s.inner * dtype.itemsize
+        return n
+
+    @staticmethod
+    def load_from_model_path(model_path: str) -> "NaforaxModelConfig":
+        with open(os.path.join(model_path, "config.json"), "r", encoding="utf-8") as f:
+            return NaforaxModelConfig(json.load(f))

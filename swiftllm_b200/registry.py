@@ -5,6 +5,7 @@
     bupozen     "architecture": "Bupozen"                   BupozenModelConfig     worker.bupozen_model.BupozenModel
     rivudra     "architecture": "Rivudra"                   RivudraModelConfig     worker.rivudra_model.RivudraModel
     buzarax     "architecture": "Buzarax"                   BuzaraxModelConfig     worker.buzarax_model.BuzaraxModel
+    naforax     "architecture": "Naforax"                   NaforaxModelConfig     worker.naforax_model.NaforaxModel
 
 Every worker class has the same public surface (load_weights, profile_num_blocks, init_kvcache_and_swap, forward /
 forward_async with the prefill-chunks-then-decodes batch layout, free_seqs_resources), so schedulers, examples and
@@ -26,6 +27,8 @@ _FAMILIES = {
                 "swiftllm_b200.model_config:RivudraModelConfig", "swiftllm_b200.worker.rivudra_model:RivudraModel"),
     "buzarax": (lambda raw: raw.get("architecture") == "Buzarax",
                 "swiftllm_b200.model_config:BuzaraxModelConfig", "swiftllm_b200.worker.buzarax_model:BuzaraxModel"),
+    "naforax": (lambda raw: raw.get("architecture") == "Naforax",
+                "swiftllm_b200.model_config:NaforaxModelConfig", "swiftllm_b200.worker.naforax_model:NaforaxModel"),
 }
 
 

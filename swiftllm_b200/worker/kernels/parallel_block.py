@@ -78,16 +78,18 @@ def moe_route_grouped(logits: torch.Tensor, top: int, groups: int, keep: int, sc
 
 
 def moe_clamped_glu_scale(u: torch.Tensor, weights, experts: int, ff: int, limit: float, shared_ff: int, shared_limit: float,
-                          alpha: float) -> torch.Tensor:
+                          alpha: float, shared_gated: bool = False) -> torch.Tensor:
     """u [T, 2 * (experts * ff + shared_ff)]: per expert [gate | up], then the shared expert's [gate | up] ->
     y [T, experts * ff + shared_ff] = min(gate, limit) * sigmoid(alpha * .) * (clamp(up, +-limit) + 1) * weights[t, expert]
-    (the shared expert: its own limit, weight 1)."""
+    (the shared expert: its own limit, weight 1 - or, with shared_gated, the extra last column of weights [T, experts + 1])."""
     assert u.is_contiguous() and (weights is None or (weights.dtype == torch.float32 and weights.is_contiguous()))
     _lib.require_device(u)
     T, cols = u.shape[0], experts * ff + shared_ff
-    assert u.shape == (T, 2 * cols) and (experts == 0 or weights.shape == (T, experts))
+    assert u.shape == (T, 2 * cols) and (weights is None or weights.shape == (T, experts + (1 if shared_gated else 0)))
+    assert weights is not None or (experts == 0 and not shared_gated)
     y = torch.empty((T, cols), dtype=u.dtype, device=u.device)
     _lib.check(_lib.lib().sllm_moe_clamped_glu_scale(u.data_ptr(), _lib.ptr(weights), y.data_ptr(), T, experts, ff, limit, shared_ff,
-                                                     shared_limit, alpha, _lib.dtype_tag_f32(u.dtype), _lib.stream()),
+                                                     shared_limit, alpha, 1 if shared_gated else 0, _lib.dtype_tag_f32(u.dtype),
+                                                     _lib.stream()),
                "moe_clamped_glu_scale")
     return y

@@ -311,6 +311,105 @@ def load_buzarax_weights(model_config, dtype: torch.dtype, model_path: Optional[
     return weight
 
 
+class NaforaxLayerWeight:
+    """One sandwich block.  Checkpoint names: `l<i>.{norm1, norm1b, norm2, norm2b}` ([width]), `l<i>.{canon1, canon2}` ([width,
+    taps]), and
+    mixer "attention": `l<i>.mix.{q, q.b, k, k.b, v, v.b, q.norm, k.norm, lq1, lk1, lq2, lk2, g, o, o.b}` (q rows head by head as
+    [map 0 | map 1], k likewise);  mixer "mingru": `l<i>.mix.{z, z.b, x, x.b, g, o}`;
+    mixer "mamba1": `l<i>.mix.{in, conv, conv.b, x, dt, dt.b, A_log, D, o}`;
+    feed-forward: `l<i>.mlp.{gate, up, down}` or `l<i>.mlp.{router, e<k>.{gate, up, down}, shared.{gate, up, down, sg}}`.
+    Fusions made at load time: every projection that reads the sublayer's input is one GEMM operand with one bias vector
+    (`in_proj`, `in_bias`: [q ; k ; v ; g] or [z ; x ; g]); the q rows are reordered to [key/value head][map][head of the group]
+    so that the attention kernel sees every map as a query head of its own whose key head is (key/value head, map);
+    `lam` = exp(lq1 . lk1) - exp(lq2 . lk2) + diff (fp32, one number); the experts' [gate ; up] rows and down columns are
+    concatenated expert by expert with the shared expert last; the router and the shared expert's gate row are one fp32 operand.
+    Norm weights, convolution taps, `A` = -exp(A_log), `D`, the step bias and the router are fp32."""
+
+    def __init__(self, layer_id: int, model_config, dtype: torch.dtype):
+        self.layer_id, self.model_config, self.dtype = layer_id, model_config, dtype
+
+    def load_weights(self, getter: Callable, device):
+        from swiftllm_b200.model_config import MinGruSpec, SelectiveScanSpec
+        c, i = self.model_config, self.layer_id
+        m, f, W, K = c.mixers[i], c.ffs[i], c.hidden_size, c.canon_taps
+
+        def get(name, shape, dtype=None):
+            w = getter(f"l{i}.{name}", shape, dtype or self.dtype)
+            assert isinstance(w, torch.Tensor) and tuple(w.shape) == tuple(shape), f"l{i}.{name}: expected shape {tuple(shape)}"
+            return w.to(device=device, dtype=dtype or self.dtype).contiguous()
+
+        f32 = torch.float32
+        self.norm1, self.norm1b, self.canon1 = get("norm1", (W,), f32), get("norm1b", (W,), f32), get("canon1", (W, K), f32)
+        if isinstance(m, MinGruSpec):
+            C = m.width
+            self.in_proj = torch.cat([get("mix.z", (C, W)), get("mix.x", (C, W)), get("mix.g", (C, W))], dim=0).contiguous()
+            self.in_bias = torch.cat([get("mix.z.b", (C,)), get("mix.x.b", (C,)), torch.zeros((C,), dtype=self.dtype, device=device)])
+            self.o = get("mix.o", (W, C))
+        elif isinstance(m, SelectiveScanSpec):
+            C, N, R = m.inner, m.state, m.dt_rank
+            self.in_proj = get("mix.in", (2 * C, W))
+            self.conv, self.conv_b = get("mix.conv", (C, m.conv), f32), get("mix.conv.b", (C,), f32)
+            self.x_proj = get("mix.x", (R + 2 * N, C))
+            self.dt_proj, self.dt_bias = get("mix.dt", (C, R)), get("mix.dt.b", (C,), f32)
+            self.A = (-torch.exp(get("mix.A_log", (C, N), f32))).contiguous()
+            self.D = get("mix.D", (C,), f32)
+            self.o = get("mix.o", (W, C))
+        else:
+            H, G, dk, dv = m.heads, m.kv_heads, m.dim, m.vdim
+            hq = H // G
+            # rows [h][map][dk] with h = g hq + hh  ->  [g][map][hh][dk]
+            order = torch.arange(H * m.maps * dk, device=device).view(G, hq, m.maps, dk).permute(0, 2, 1, 3).reshape(-1)
+            q, qb = get("mix.q", (H * m.maps * dk, W)), get("mix.q.b", (H * m.maps * dk,))
+            self.in_proj = torch.cat([q[order], get("mix.k", (G * m.maps * dk, W)), get("mix.v", (G * dv, W)),
+                                      get("mix.g", (H * dv, W))], dim=0).contiguous()
+            self.in_bias = torch.cat([qb[order], get("mix.k.b", (G * m.maps * dk,)), get("mix.v.b", (G * dv,)),
+                                      torch.zeros((H * dv,), dtype=self.dtype, device=device)]).contiguous()
+            self.q_norm, self.k_norm = get("mix.q.norm", (dk,), f32), get("mix.k.norm", (dk,), f32)
+            lq1, lk1, lq2, lk2 = (get(f"mix.{n}", (dk,), f32) for n in ("lq1", "lk1", "lq2", "lk2"))
+            self.lam = float(torch.exp((lq1 * lk1).sum()) - torch.exp((lq2 * lk2).sum()) + m.diff)
+            self.o, self.o_bias = get("mix.o", (W, H * dv)), get("mix.o.b", (W,))
+        if f is None:
+            return
+        self.norm2, self.norm2b, self.canon2 = get("norm2", (W,), f32), get("norm2b", (W,), f32), get("canon2", (W, K), f32)
+        if f.kind == "dense":
+            self.up = torch.cat([get("mlp.gate", (f.ff, W)), get("mlp.up", (f.ff, W))], dim=0).contiguous()
+            self.down = get("mlp.down", (W, f.ff))
+        else:
+            rows = [get("mlp.router", (f.experts, W), f32)] + ([get("mlp.shared.sg", (1, W), f32)] if f.shared_gated else [])
+            self.router = torch.cat(rows, dim=0).contiguous()                                        # the router runs in fp32
+            names = [(f"mlp.e{e}", f.ff) for e in range(f.experts)] + ([("mlp.shared", f.shared_ff)] if f.shared_ff else [])
+            self.up = torch.cat([get(f"{n}.{part}", (ff, W)) for n, ff in names for part in ("gate", "up")], dim=0).contiguous()
+            self.down = torch.cat([get(f"{n}.down", (W, ff)) for n, ff in names], dim=1).contiguous()
+
+
+class NaforaxWeight:
+    def __init__(self, model_config, dtype: torch.dtype):
+        self.model_config, self.dtype = model_config, dtype
+        self.layers = [NaforaxLayerWeight(i, model_config, dtype) for i in range(model_config.num_layers)]
+
+    def load_weights(self, getter: Callable, device="cuda"):
+        c = self.model_config
+        vs = (c.vocab_size, c.hidden_size)
+        self.wte = getter("embed", vs, self.dtype).to(device=device, dtype=self.dtype).contiguous()
+        self.loop_step = None
+        if c.loop is not None:
+            self.loop_step = getter("loop.step", (c.loop[2], c.hidden_size), torch.float32).to(device=device, dtype=torch.float32).contiguous()
+        self.final_norm = getter("final.norm", (c.hidden_size,), torch.float32).to(device=device, dtype=torch.float32).contiguous()
+        self.lm_head = getter("head", vs, self.dtype).to(device=device, dtype=self.dtype).contiguous()
+        self.lm_head_sharded = False
+        for layer in self.layers:
+            layer.load_weights(getter, device)
+
+
+def load_naforax_weights(model_config, dtype: torch.dtype, model_path: Optional[str], use_dummy: bool = False,
+                         getter: Optional[Callable] = None, device="cuda") -> NaforaxWeight:
+    if getter is None:
+        getter = dummy_getter(device) if use_dummy else checkpoint_getter(model_path, device)
+    weight = NaforaxWeight(model_config, dtype)
+    weight.load_weights(getter, device)
+    return weight
+
+
 # ---------------------------------------------------------------- getters
 def dummy_getter(device="cuda"):
     """weight.py:215-218: uniform(-1e-3, 1e-3), unseeded ("mainly for profiling")."""

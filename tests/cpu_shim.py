@@ -217,7 +217,7 @@ def _moe_route_grouped(logits, top, groups, keep, scale, norm_eps):
     return torch.zeros_like(s).scatter_(1, idx, w / (w.sum(-1, keepdim=True) + norm_eps) * scale)
 
 
-def _moe_clamped_glu_scale(u, weights, experts, ff, limit, shared_ff, shared_limit, alpha):
+def _moe_clamped_glu_scale(u, weights, experts, ff, limit, shared_ff, shared_limit, alpha, shared_gated=False):
     T = u.shape[0]
     uf = u.float()
 
@@ -226,9 +226,9 @@ def _moe_clamped_glu_scale(u, weights, experts, ff, limit, shared_ff, shared_lim
         return g * torch.sigmoid(alpha * g) * (v + 1.0)
     parts = []
     if experts:
-        parts.append((act(uf[:, :2 * experts * ff].view(T, experts, 2 * ff), ff, limit) * weights[:, :, None]).reshape(T, experts * ff))
+        parts.append((act(uf[:, :2 * experts * ff].view(T, experts, 2 * ff), ff, limit) * weights[:, :experts, None]).reshape(T, experts * ff))
     if shared_ff:
-        parts.append(act(uf[:, 2 * experts * ff:], shared_ff, shared_limit))
+        parts.append(act(uf[:, 2 * experts * ff:], shared_ff, shared_limit) * (weights[:, experts:experts + 1] if shared_gated else 1.0))
     return torch.cat(parts, dim=1).to(u.dtype)
 
 
@@ -255,7 +255,10 @@ def _unit_rms(x, eps):
 def _window_kv_store(k, v, cache, slot, block_table, st, kv_heads, dk, dv, rot_dims, cos, sin, opt=None, vcos=None, vsin=None):
     T = k.shape[0]
     halves = bool(opt and opt.pair_halves)
-    kr = _rot_any(k.float().view(T, kv_heads, dk), cos, sin, rot_dims, halves)
+    kr = k.float().view(T, kv_heads, dk)
+    if opt and opt.k_norm is not None:
+        kr = _unit_rms(kr, opt.prenorm_eps) * opt.k_norm
+    kr = _rot_any(kr, cos, sin, rot_dims, halves)
     if opt and opt.qk_norm_eps >= 0:
         kr = _unit_rms(kr, opt.qk_norm_eps)
     kr = kr.reshape(T, kv_heads * dk).to(k.dtype)
@@ -270,16 +273,22 @@ def _window_attention(q, gate, cache, slot, block_table, st, out, heads, kv_head
                       opt=None, vcos=None, vsin=None):
     T = q.shape[0]
     halves = bool(opt and opt.pair_halves)
-    qa = _rot_any(q.float().view(T, heads, dk), cos, sin, rot_dims, halves)
+    qa = q.float().view(T, heads, dk)
+    if opt and opt.q_norm is not None:
+        qa = _unit_rms(qa, opt.prenorm_eps) * opt.q_norm
+    qa = _rot_any(qa, cos, sin, rot_dims, halves)
     if opt and opt.qk_norm_eps >= 0:
         qa = _unit_rms(qa, opt.qk_norm_eps)
     qa = qa * scale
     rep = heads // kv_heads
+    vshare = opt.vshare if opt else 1
     for t, (sq, p) in enumerate(zip(st.token_seq_ids.tolist(), st.token_positions.tolist())):
         lo = max(0, p - window + 1) if window > 0 else 0
-        rows = _cache_rows(cache, slot, block_table, sq, list(range(lo, p + 1))).float()      # [n, G (dk + dv)]
+        if opt and opt.chunk > 0:
+            lo = max(lo, p // opt.chunk * opt.chunk)
+        rows = _cache_rows(cache, slot, block_table, sq, list(range(lo, p + 1))).float()      # [n, G dk + G / vshare dv]
         ks = rows[:, :kv_heads * dk].view(-1, kv_heads, dk).repeat_interleave(rep, dim=1)     # [n, H, dk]
-        vs = rows[:, kv_heads * dk:].view(-1, kv_heads, dv).repeat_interleave(rep, dim=1)
+        vs = rows[:, kv_heads * dk:].view(-1, kv_heads // vshare, dv).repeat_interleave(rep * vshare, dim=1)
         sc = torch.einsum("hd,nhd->hn", qa[t], ks)
         if opt and opt.softcap > 0:
             sc = opt.softcap * torch.tanh(sc / opt.softcap)
@@ -293,6 +302,124 @@ def _window_attention(q, gate, cache, slot, block_table, st, out, heads, kv_head
         if gate is not None:
             o = o * torch.sigmoid(gate[t].float())
         out[t] = o.to(out.dtype)
+
+
+def _diff_combine(a, gate, out, heads, kv_heads, dv, lam, eps, factor):
+    T, hq = a.shape[0], heads // kv_heads
+    maps = a.view(T, kv_heads, 2, hq, dv)
+    o = _unit_rms(maps[:, :, 0] - lam * maps[:, :, 1], eps).reshape(T, heads * dv) * factor
+    if gate is not None:
+        o = o * torch.sigmoid(gate.float())
+    out.copy_(o.to(out.dtype))
+
+
+# ---------------------------------------------------------------- stand-ins of the sandwich-block kernels
+def _group_rms(x, groups, eps):
+    T, W = x.shape
+    return _unit_rms(x.view(T, groups, W // groups), eps).reshape(T, W)
+
+
+def _group_norm_add_norm(x, y, wb, mult, wn, eps, groups, n_out=None):
+    if y is not None:
+        x += mult * _group_rms(y.float(), groups, eps) * wb
+    if wn is None:
+        return None
+    n = _group_rms(x, groups, eps) * wn
+    if n_out is not None:
+        n_out.copy_(n)
+        return n_out
+    return n
+
+
+def _group_norm_cast(x, w, eps, groups, out_dtype):
+    return (_group_rms(x, groups, eps) * w).to(out_dtype)
+
+
+def _stream_add(x, a=None, v=None):
+    if a is not None:
+        x += a
+    if v is not None:
+        x += v
+
+
+def _gelu_glu(u):
+    F = u.shape[1] // 2
+    uf = u.float()
+    return (torch.nn.functional.gelu(uf[:, :F], approximate="tanh") * uf[:, F:]).to(u.dtype)
+
+
+def _moe_route_softmax(logits, experts, top, gated):
+    s = torch.softmax(logits[:, :experts], dim=-1)
+    idx = torch.sort(s, dim=-1, descending=True, stable=True).indices[:, :top]
+    w = torch.zeros_like(logits)
+    w[:, :experts] = torch.zeros_like(s).scatter_(1, idx, s.gather(1, idx))
+    if gated:
+        w[:, experts] = torch.sigmoid(logits[:, experts])
+    return w
+
+
+def _linear_f32_out(a, w):
+    return a.float() @ w.float().t()
+
+
+def _short_conv(xin, w, bias, tail, st, out_dtype, add_input=False, silu=False):
+    T, C = xin.shape
+    K = w.shape[1]
+    xf = xin.float()
+    out = torch.zeros((T, C))
+    pos = st.token_positions.tolist()
+    for sq, lo, hi in _segments(st):
+        for t in range(lo, hi):
+            acc = torch.zeros(C) if bias is None else bias.clone()
+            for k in range(K):
+                if pos[t] - k < 0:
+                    continue
+                src = xf[t - k] if t - k >= lo else tail[sq, K - 1 - (k - (t - lo))].float()
+                acc = acc + w[:, K - 1 - k] * src
+            if silu:
+                acc = torch.nn.functional.silu(acc)
+            out[t] = acc + (xf[t] if add_input else 0.0)
+    return out.to(out_dtype)
+
+
+def _conv_tail_update(xin, tail, st):
+    K = tail.shape[1] + 1
+    pos = st.token_positions.tolist()
+    for sq, lo, hi in _segments(st):
+        old = tail[sq].clone() if pos[lo] > 0 else torch.zeros_like(tail[sq])
+        hist = torch.cat([old, xin[lo:hi].to(tail.dtype)], dim=0)
+        tail[sq] = hist[-(K - 1):]
+
+
+def _mingru_scan(proj, state, st, channels):
+    C = channels
+    pf = proj.float()
+    out = torch.zeros((proj.shape[0], C))
+    pos = st.token_positions.tolist()
+    for sq, lo, hi in _segments(st):
+        S = state[sq].clone() if pos[lo] > 0 else torch.zeros(C)
+        for t in range(lo, hi):
+            z, u, g = torch.sigmoid(pf[t, :C]), pf[t, C:2 * C], pf[t, 2 * C:]
+            S = (1.0 - z) * S + z * torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+            out[t] = S * torch.nn.functional.silu(g)
+        state[sq] = S
+    return out.to(proj.dtype)
+
+
+def _selective_scan(x, dt, dt_bias, A, bc, b_off, c_off, D, z, state, st):
+    T, C = x.shape
+    N = A.shape[1]
+    xf, zf, bcf = x.float(), z.float(), bc.float()
+    step = torch.nn.functional.softplus(dt.float() + dt_bias)
+    out = torch.zeros((T, C))
+    pos = st.token_positions.tolist()
+    for sq, lo, hi in _segments(st):
+        S = state[sq].clone() if pos[lo] > 0 else torch.zeros((C, N))
+        for t in range(lo, hi):
+            S = torch.exp(step[t][:, None] * A) * S + (step[t] * xf[t])[:, None] * bcf[t, b_off:b_off + N][None, :]
+            out[t] = ((S * bcf[t, c_off:c_off + N][None, :]).sum(1) + D * xf[t]) * torch.nn.functional.silu(zf[t])
+        state[sq] = S
+    return out.to(x.dtype)
 
 
 # ---------------------------------------------------------------- stand-ins of the sequential-block / recurrent kernels
@@ -486,6 +613,22 @@ _PATCHES = [
     ("swiftllm_b200.worker.layers.gated_recurrence", "rglru_scan", _rglru_scan),
     ("swiftllm_b200.worker.layers.linear_attention", "linear_attention", _linear_attention),
     ("swiftllm_b200.worker.layers.linear_attention", "gated_rmsnorm", _gated_rmsnorm),
+    ("swiftllm_b200.worker.layers.window_attention", "diff_combine", _diff_combine),
+    ("swiftllm_b200.worker.naforax_model", "embed_pair_hash", _embed_pair_hash),
+    ("swiftllm_b200.worker.naforax_model", "tanh_cap_inplace", _tanh_cap_inplace),
+    ("swiftllm_b200.worker.naforax_model", "group_norm_add_norm", _group_norm_add_norm),
+    ("swiftllm_b200.worker.naforax_model", "group_norm_cast", _group_norm_cast),
+    ("swiftllm_b200.worker.naforax_model", "stream_add", _stream_add),
+    ("swiftllm_b200.worker.layers.sandwich_block", "group_norm_add_norm", _group_norm_add_norm),
+    ("swiftllm_b200.worker.layers.sandwich_block", "short_conv", _short_conv),
+    ("swiftllm_b200.worker.layers.sandwich_block", "conv_tail_update", _conv_tail_update),
+    ("swiftllm_b200.worker.layers.selective_scan", "short_conv", _short_conv),
+    ("swiftllm_b200.worker.layers.selective_scan", "conv_tail_update", _conv_tail_update),
+    ("swiftllm_b200.worker.layers.selective_scan", "selective_scan", _selective_scan),
+    ("swiftllm_b200.worker.layers.selective_scan", "linear_f32_out", _linear_f32_out),
+    ("swiftllm_b200.worker.layers.min_gru", "mingru_scan", _mingru_scan),
+    ("swiftllm_b200.worker.layers.feed_forward", "gelu_glu", _gelu_glu),
+    ("swiftllm_b200.worker.layers.feed_forward", "moe_route_softmax", _moe_route_softmax),
     ("swiftllm_b200.worker.layers.feed_forward", "moe_route", _moe_route),
     ("swiftllm_b200.worker.layers.feed_forward", "moe_relu2_scale_inplace", _moe_relu2_scale_inplace),
 ]
