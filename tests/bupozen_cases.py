@@ -10,9 +10,10 @@ import torch
 
 from oracle import bupozen as O
 from oracle import buzarax as _buzarax
+from oracle import naforax as _naforax
 from oracle import rivudra as _rivudra
 
-_ORACLES = {"Bupozen": O, "Rivudra": _rivudra, "Buzarax": _buzarax}
+_ORACLES = {"Bupozen": O, "Rivudra": _rivudra, "Buzarax": _buzarax, "Naforax": _naforax}
 
 
 def oracle_of(cfg):
