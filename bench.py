@@ -4,7 +4,7 @@
   python bench.py [--gpus N] [--steps K] [--warmup W]            # this implementation
   python bench.py --impl reference ...                            # CPU arm: torch-eager oracle port on host cores
   torchrun --nproc-per-node N bench.py --gpus N ...               # N > 1: tensor parallel (heads / FFN columns)
-  python bench.py --arch-compare all [--steps K] [--warmup W]     # NOT the headline: Bupozen / Rivudra / Buzarax workers beside the Llama worker
+  python bench.py --arch-compare all [--steps K] [--warmup W]     # NOT the headline: Bupozen / Rivudra / Buzarax / Naforax workers beside the Llama worker
                                                                   # (prefill / decode tok/s, attention roofline), 1 GPU
 
 Workload (BASELINE.json configs[1]): Llama-3-8B shapes, bf16, pure decode, batch 256, every sequence at
@@ -88,7 +88,7 @@ def parse():
     ap.add_argument("--no-live-traffic", action="store_true", help="skip the ncu DRAM-byte measurement of the decode kernel")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--arch-models", type=str, default="", metavar="NAMES",
-                    help="with --arch-compare: only these workers (comma-separated: bupozen, rivudra, buzarax, llama); default all")
+                    help="with --arch-compare: only these workers (comma-separated: bupozen, rivudra, buzarax, naforax, llama); default all")
     ap.add_argument("--arch-compare", type=str, default="", metavar="SIZES",
                     help="instead of the headline workload: prefill and decode throughput of the Bupozen and Rivudra workers beside the "
                          "Llama worker at equal width / depth (random weights), with the attention kernels' roofline fractions; "
@@ -150,7 +150,20 @@ def _arch_models(sz, dtype, only=None):
                   {"type": "rglru", "mixer": {"width": W, "blocks": H, "conv": 4}, "mlp": buz_moe} for i in range(sz["layers"])]
     buz = {"architecture": "Buzarax", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31}}, "layers": buz_layers}
-    for name, raw in (("bupozen", bup), ("rivudra", riv), ("buzarax", buz), ("llama", llama)):
+    # Naforax: [differential attention (heads / 4 KV heads, two maps of 64 per head, values of 128, chunks of the window's size) +
+    # dense ff], [minGRU of the model's width + experts], [selective scan (inner 2 W, 16 states, 4 taps) + experts], [attention +
+    # experts]; experts with a gated shared expert; the middle two layers are the repeated range (one pass: equal depth)
+    nattn = {"heads": H, "kv_heads": G, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.3, "mask": {"size": sz["window"]},
+             "rot": {"base": 10000.0, "dims": 32}}
+    naf_moe = {"kind": "moe", "expert": {"ff": sz["eff"], "limit": 7.0}, "shared": {"ff": sz["eff"], "limit": 7.0},
+               "router": {"experts": sz["experts"], "top": sz["top"]}}
+    naf_mixers = [("attention", nattn), ("mingru", {"width": W}),
+                  ("mamba1", {"inner": 2 * W, "state": 16, "dt_rank": W // 16, "conv": 4}), ("attention", nattn)]
+    naf = {"architecture": "Naforax", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-5, "groups": 2}, "residual_mult": 0.7,
+           "logit_softcap": 30.0, "canon": {"taps": 3}, "loop": {"start": 1, "stop": 3, "times": 1},
+           "layers": [{"type": naf_mixers[i % 4][0], "mixer": naf_mixers[i % 4][1],
+                       "mlp": {"kind": "dense", "ff": sz["ff"]} if i == 0 else naf_moe} for i in range(sz["layers"])]}
+    for name, raw in (("bupozen", bup), ("rivudra", riv), ("buzarax", buz), ("naforax", naf), ("llama", llama)):
         if only and name not in only:
             continue
         ec = swiftllm_b200.EngineConfig(model_path="", use_dummy=False, block_size=16, gpu_mem_utilization=0.9, num_cpu_blocks=0,
@@ -210,7 +223,7 @@ def run_arch_compare(args):
             layers_pkg = "swiftllm_b200.worker.layers."
             if name == "bupozen":
                 mod, attrs = importlib.import_module(layers_pkg + "latent_attention"), ["latent_attention"]
-            elif name in ("rivudra", "buzarax"):
+            elif name in ("rivudra", "buzarax", "naforax"):
                 mod, attrs = importlib.import_module(layers_pkg + "window_attention"), ["window_attention"]
             else:
                 mod, attrs = importlib.import_module(layers_pkg + "transformer_layer"), ["prefill_attention", "paged_attention"]
@@ -220,6 +233,13 @@ def run_arch_compare(args):
                 extra = {"linear_attention": (importlib.import_module(layers_pkg + "linear_attention"), "linear_attention"),
                          "rglru_scan": (importlib.import_module(layers_pkg + "gated_recurrence"), "rglru_scan"),
                          "causal_conv": (importlib.import_module(layers_pkg + "gated_recurrence"), "causal_conv")}
+            if name == "naforax":
+                extra = {"mingru_scan": (importlib.import_module(layers_pkg + "min_gru"), "mingru_scan"),
+                         "selective_scan": (importlib.import_module(layers_pkg + "selective_scan"), "selective_scan"),
+                         "scan_conv": (importlib.import_module(layers_pkg + "selective_scan"), "short_conv"),
+                         "input_conv": (importlib.import_module(layers_pkg + "sandwich_block"), "short_conv"),
+                         "group_norms": (importlib.import_module(layers_pkg + "sandwich_block"), "group_norm_add_norm"),
+                         "diff_combine": (importlib.import_module(layers_pkg + "window_attention"), "diff_combine")}
             extra_ms = {}
 
             def timed(fn, steps, warmup, after=None):
@@ -304,6 +324,34 @@ def run_arch_compare(args):
                     "rglru_scan": (Lr * ntok * Wd * 30, Lr * ntok * Wd * 10, Lr * dec_batch * Wd * 30, Lr * dec_batch * Wd * (10 + 8 + 12)),
                     "causal_conv": (Lr * ntok * Wd * 8, Lr * ntok * Wd * 4, Lr * dec_batch * Wd * 8, Lr * dec_batch * Wd * (4 + 6)),
                 }
+            elif name == "naforax":
+                # attention layers 0 and 3 of every four; two maps of dk = 64 per head over values of dv = 128; a query sees its
+                # chunk only.  Prefill bytes: q (2 bytes), the maps' fp32 outputs, the cache rows once; decode: the visible rows.
+                kinds = [i % 4 for i in range(L)]
+                La, Lg, Ls = sum(k in (0, 3) for k in kinds), kinds.count(1), kinds.count(2)
+                Lff = L                                                    # every layer has a feed-forward
+                dk, dv, nkv, Wd, Ck, Ns = 64, 128, max(1, H // 4), sz["width"], sz["window"], 16
+                ntok, Ci = n_prompts * prompt_len, 2 * sz["width"]
+                vis_pre = sum(p % Ck + 1 for p in range(prompt_len)) * n_prompts
+                vis_dec = dec_batch * (ctx % Ck + 1)
+                row = nkv * (2 * dk + dv) * 2
+                fl_pre, by_pre = La * vis_pre * 2 * H * (2 * dk + 2 * dv), La * ntok * (2 * H * dk * 2 + 2 * H * dv * 4 + row)
+                fl_dec, by_dec = La * vis_dec * 2 * H * (2 * dk + 2 * dv), La * vis_dec * row
+                # label -> (prefill FLOPs, bytes, decode FLOPs, bytes).  minGRU: three logits in, the product out (2 bytes each);
+                # decode adds the fp32 state both ways.  selective scan: x, z in and the product out (2 bytes), fp32 step logits,
+                # 7 operations per state entry and token; decode adds the fp32 state both ways.  Convolutions: fp32 in (input
+                # convolution) or 2 bytes in (the scan's), 2 bytes out, 2 * taps operations; decode adds the tail both ways.
+                # Group norms: the stream both ways, the sublayer's output in, the next norm out (fp32).
+                nconv = L + Lff
+                extra_roof = {
+                    "mingru_scan": (Lg * ntok * Wd * 20, Lg * ntok * Wd * 8, Lg * dec_batch * Wd * 20, Lg * dec_batch * Wd * 16),
+                    "selective_scan": (Ls * ntok * Ci * 7 * Ns, Ls * ntok * Ci * 10, Ls * dec_batch * Ci * 7 * Ns,
+                                       Ls * dec_batch * Ci * (10 + 8 * Ns)),
+                    "scan_conv": (Ls * ntok * Ci * 8, Ls * ntok * Ci * 4, Ls * dec_batch * Ci * 8, Ls * dec_batch * Ci * (4 + 6)),
+                    "input_conv": (nconv * ntok * Wd * 6, nconv * ntok * Wd * 6, nconv * dec_batch * Wd * 6, nconv * dec_batch * Wd * (6 + 8)),
+                    "group_norms": (nconv * ntok * Wd * 8, nconv * ntok * Wd * 14, nconv * dec_batch * Wd * 8, nconv * dec_batch * Wd * 14),
+                    "diff_combine": (La * ntok * H * dv * 8, La * ntok * H * dv * 12, La * dec_batch * H * dv * 8, La * dec_batch * H * dv * 12),
+                }
             else:
                 D, nkv = sz["width"] // H, max(1, H // 4)
                 fl_pre = L * n_prompts * (prompt_len * (prompt_len + 1) // 2) * H * D * 4
@@ -315,7 +363,7 @@ def run_arch_compare(args):
                 t_min = max(fl / (peaks["bf16_tflops"] * 1e12), by / (peaks["hbm_gbs"] * 1e9)) * 1e3
                 return round(t_min / ms, 4) if ms > 0 else None
             other = {}
-            if name == "buzarax":
+            if name in ("buzarax", "naforax"):
                 for k, (fp, bp, fd, bd) in extra_roof.items():
                     other[k] = {"prefill_ms": round(pre_extra.get(k, 0.0), 3), "decode_ms": round(dec_extra.get(k, 0.0), 3),
                                 "prefill_roofline_frac": roof(fp, bp, pre_extra.get(k, 0.0)),
