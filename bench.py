@@ -109,6 +109,9 @@ ARCH_SIZES = {
 }
 
 
+NAFORAX_CHUNK = 8192      # positions per attention chunk: longer than the benchmark's sequences, so the mask is plain causal here
+
+
 def _arch_models(sz, dtype, only=None):
     """(name, worker) pairs: Rivudra (gated sliding-window GQA attention with heads / 4 KV heads, every layer a mixture of experts
     with a shared expert), Bupozen (layers alternate own-latent + dense ff / borrowed latent + MoE) and the closest existing
@@ -150,10 +153,10 @@ def _arch_models(sz, dtype, only=None):
                   {"type": "rglru", "mixer": {"width": W, "blocks": H, "conv": 4}, "mlp": buz_moe} for i in range(sz["layers"])]
     buz = {"architecture": "Buzarax", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31}}, "layers": buz_layers}
-    # Naforax: [differential attention (heads / 4 KV heads, two maps of 64 per head, values of 128, chunks of the window's size) +
+    # Naforax: [differential attention (heads / 4 KV heads, two maps of 64 per head, values of 128, chunks of 8192 positions) +
     # dense ff], [minGRU of the model's width + experts], [selective scan (inner 2 W, 16 states, 4 taps) + experts], [attention +
     # experts]; experts with a gated shared expert; the middle two layers are the repeated range (one pass: equal depth)
-    nattn = {"heads": H, "kv_heads": G, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.3, "mask": {"size": sz["window"]},
+    nattn = {"heads": H, "kv_heads": G, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.3, "mask": {"size": NAFORAX_CHUNK},
              "rot": {"base": 10000.0, "dims": 32}}
     naf_moe = {"kind": "moe", "expert": {"ff": sz["eff"], "limit": 7.0}, "shared": {"ff": sz["eff"], "limit": 7.0},
                "router": {"experts": sz["experts"], "top": sz["top"]}}
@@ -330,7 +333,7 @@ def run_arch_compare(args):
                 kinds = [i % 4 for i in range(L)]
                 La, Lg, Ls = sum(k in (0, 3) for k in kinds), kinds.count(1), kinds.count(2)
                 Lff = L                                                    # every layer has a feed-forward
-                dk, dv, nkv, Wd, Ck, Ns = 64, 128, max(1, H // 4), sz["width"], sz["window"], 16
+                dk, dv, nkv, Wd, Ck, Ns = 64, 128, max(1, H // 4), sz["width"], NAFORAX_CHUNK, 16
                 ntok, Ci = n_prompts * prompt_len, 2 * sz["width"]
                 vis_pre = sum(p % Ck + 1 for p in range(prompt_len)) * n_prompts
                 vis_dec = dec_batch * (ctx % Ck + 1)

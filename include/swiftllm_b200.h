@@ -392,18 +392,22 @@ int sllm_moe_route_softmax(const void* logits, void* weights, int64_t num_tokens
  * elements); z = sigmoid, c = u + 1/2 (u >= 0) | sigmoid(u); S <- (1 - z) S + z c; out = S * silu(g); state fp32 [rows, channels].
  * selective_scan: x, z dtype [T, channels]; dt [T, channels] step logits (fp32 when dt_f32, else dtype); bc rows hold B at
  * column b_off and C at c_off (`states` each); A fp32 [channels, states]; dt = softplus(dt + dt_bias);
- * S[c, n] <- exp(dt A) S + dt x B[n]; out = (sum_n S C[n] + D x) * silu(z); state fp32 [rows, channels, states]; states <= 256. */
+ * S[c, n] <- exp(dt A) S + dt x B[n]; out = (sum_n S C[n] + D x) * silu(z); state fp32 [rows, channels, states]; states <= 256.
+ * Both scans: the first num_prefill_segs segments (prompt portions) run through kernels that stage or split tiles of tokens
+ * (minGRU: 64 tokens as eight composed runs; selective scan: 16 tokens staged in shared memory), the rest (single decoded tokens)
+ * one thread per channel (and state slice); any value in 0 .. num_segs gives the same result up to rounding. */
 int sllm_short_conv(const void* xin, int64_t xin_stride, sllm_dtype_t in_dtype, const void* w, const void* bias, const void* tail,
                     const void* tok_seq, const void* tok_pos, void* out, sllm_dtype_t out_dtype, int64_t num_tokens,
                     int64_t num_prefill_tokens, int channels, int taps, int add_input, int act_silu, sllm_stream_t stream);
 int sllm_conv_tail_update(const void* xin, int64_t xin_stride, void* tail, const void* seg_starts, const void* seq_ids,
                           const void* tok_pos, int num_segs, int channels, int taps, sllm_dtype_t dtype, sllm_stream_t stream);
 int sllm_mingru_scan(const void* proj, int64_t proj_stride, void* state, const void* seg_starts, const void* seq_ids,
-                     const void* tok_pos, void* out, int num_segs, int channels, sllm_dtype_t dtype, sllm_stream_t stream);
+                     const void* tok_pos, void* out, int num_segs, int num_prefill_segs, int channels, sllm_dtype_t dtype,
+                     sllm_stream_t stream);
 int sllm_selective_scan(const void* x, int64_t x_stride, const void* dt, int64_t dt_stride, int dt_f32, const void* dt_bias,
                         const void* A, const void* bc, int64_t bc_stride, int b_off, int c_off, const void* D, const void* z,
                         int64_t z_stride, void* state, const void* seg_starts, const void* seq_ids, const void* tok_pos, void* out,
-                        int num_segs, int channels, int states, sllm_dtype_t dtype, sllm_stream_t stream);
+                        int num_segs, int num_prefill_segs, int channels, int states, sllm_dtype_t dtype, sllm_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -68,8 +68,8 @@ SIGNATURES = {
     "sllm_moe_route_softmax": (_I, [_P, _P, _L, _I, _I, _I, _P]),
     "sllm_short_conv": (_I, [_P, _L, _I, _P, _P, _P, _P, _P, _P, _I, _L, _L, _I, _I, _I, _I, _P]),
     "sllm_conv_tail_update": (_I, [_P, _L, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
-    "sllm_mingru_scan": (_I, [_P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
-    "sllm_selective_scan": (_I, [_P, _L, _P, _L, _I, _P, _P, _P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "sllm_mingru_scan": (_I, [_P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "sllm_selective_scan": (_I, [_P, _L, _P, _L, _I, _P, _P, _P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "sllm_embed_pair_hash": (_I, [_P, _P, _P, _P, _P, _P, _I, _L, _L, _P, _P, _P, _L, _I, _I, _P]),
     "sllm_store_last_tokens": (_I, [_P, _P, _P, _P, _I, _P]),
     "sllm_postnorm_add_mix": (_I, [_P, _P, _P, _F, _P, _I, _P, _P, _L, _I, _I, _P]),

@@ -125,6 +125,63 @@ __global__ void __launch_bounds__(128) mingru_scan_kernel(const T* __restrict__ 
     state[(int64_t)seq * C + c] = S;
 }
 
+// The same recurrence for PROMPT PORTIONS, parallel over time as well: grid (segments, ceil(C / 32)), 8 warps.  Lane: channel;
+// warp w: tokens 8 w .. 8 w + 7 of the current tile of 64 tokens.  Every thread turns its tokens' logits into the pairs (a, b) of
+// S -> a S + b (all loads of a run are issued before its sigmoids), composes its run into one such map, the eight maps of a tile
+// meet in shared memory, every warp takes the state at its run's start from the maps before it and replays its run.
+template <typename T>
+__global__ void __launch_bounds__(256) mingru_scan_tiled_kernel(const T* __restrict__ proj, int64_t stride, float* __restrict__ state,
+                                                                const int* __restrict__ seg_starts, const int* __restrict__ seq_ids,
+                                                                const int* __restrict__ tok_pos, T* __restrict__ out, int C) {
+    __shared__ float sa[8][32], sb[8][32], s0[32];
+    const int b = blockIdx.x, lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int c = blockIdx.y * 32 + lane;
+    const int t0 = seg_starts[b], n = seg_starts[b + 1] - t0;
+    if (n <= 0) return;                                 // the whole CTA
+    const bool live = c < C;
+    const int seq = seq_ids[b];
+    if (w == 0) s0[lane] = (live && tok_pos[t0] > 0) ? state[(int64_t)seq * C + c] : 0.f;
+    float S = 0.f;
+    for (int tile0 = 0; tile0 < n; tile0 += 64) {
+        const int j0 = tile0 + w * 8;
+        float a[8], bb[8], g[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {                   // raw logits first: 24 loads in flight
+            const bool ok = live && j0 + j < n;
+            const T* pr = proj + (int64_t)(t0 + j0 + j) * stride + c;
+            a[j] = ok ? ldf(pr) : 0.f;
+            bb[j] = ok ? ldf(pr + C) : 0.f;
+            g[j] = ok ? ldf(pr + 2 * C) : 0.f;
+        }
+        float A = 1.f, B = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            if (live && j0 + j < n) {
+                const float z = sigmoid_fn(a[j]), u = bb[j];
+                a[j] = 1.f - z;
+                bb[j] = z * (u >= 0.f ? u + 0.5f : sigmoid_fn(u));
+                g[j] = silu_fn(g[j]);
+            } else {
+                a[j] = 1.f; bb[j] = 0.f;                // past the segment's end: the identity map
+            }
+            B = a[j] * B + bb[j];
+            A *= a[j];
+        }
+        sa[w][lane] = A; sb[w][lane] = B;
+        __syncthreads();
+        S = s0[lane];
+        for (int k = 0; k < w; k++) S = sa[k][lane] * S + sb[k][lane];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            S = a[j] * S + bb[j];
+            if (live && j0 + j < n) stf(out + (int64_t)(t0 + j0 + j) * C + c, S * g[j]);
+        }
+        __syncthreads();                                // s0 and the maps have been read
+        if (w == 7) s0[lane] = S;                       // the tile's last run ends at the tile's end state
+    }
+    if (w == 7 && live) state[(int64_t)seq * C + c] = S;
+}
+
 // Block: 128 threads = (128 / NS) channels x NS lanes per channel; a thread holds the states n = s + NS r (r < SS_R) of its
 // channel in registers.  grid (segments, ceil(C / (128 / NS))).  x, z: T [T, C] (row strides); dtl: TD [T, C] step logits (without
 // bias); bc: T [T, ...] rows with B at column b_off and C at column c_off (N each); A fp32 [C, N] (negative); state fp32
@@ -183,6 +240,94 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(
     }
 }
 
+// The same scan for PROMPT PORTIONS with staged tiles of SS_TT tokens: all threads first bring the tile's x, step sizes (softplus
+// applied), SiLU gates and B / C rows into shared memory with coalesced loads (one exposed load latency per tile instead of one
+// per token), the sequential part then reads shared memory only, and the tile's outputs leave coalesced.  Same thread layout,
+// same arithmetic per step.  Dynamic shared memory: (4 SS_TT (128 / NS) + 2 SS_TT N) floats.
+constexpr int SS_TT = 16;
+
+template <typename T, typename TD>
+__global__ void __launch_bounds__(128) selective_scan_tiled_kernel(
+    const T* __restrict__ x, int64_t x_stride, const TD* __restrict__ dtl, int64_t dt_stride, const float* __restrict__ dt_bias,
+    const float* __restrict__ A, const T* __restrict__ bc, int64_t bc_stride, int b_off, int c_off, const float* __restrict__ D,
+    const T* __restrict__ z, int64_t z_stride, float* __restrict__ state, const int* __restrict__ seg_starts,
+    const int* __restrict__ seq_ids, const int* __restrict__ tok_pos, T* __restrict__ out, int C, int N, int ns_log2) {
+    extern __shared__ float ssm[];
+    const int NS = 1 << ns_log2, ch_log2 = 7 - ns_log2, CH = 1 << ch_log2;
+    float* xs = ssm;                                    // [SS_TT][CH]
+    float* ds = xs + SS_TT * CH;
+    float* zs = ds + SS_TT * CH;
+    float* ys = zs + SS_TT * CH;
+    float* bs = ys + SS_TT * CH;                        // [SS_TT][N]
+    float* cs = bs + SS_TT * N;
+    const int b = blockIdx.x, tid = threadIdx.x;
+    const int s = tid & (NS - 1), cl = tid >> ns_log2;
+    const int cbase = blockIdx.y * CH, c = cbase + cl;
+    const int t0 = seg_starts[b], n = seg_starts[b + 1] - t0;
+    if (n <= 0) return;
+    const bool live = c < C;
+    const int cc = live ? c : 0;
+    const int seq = seq_ids[b];
+    const bool fresh = tok_pos[t0] == 0;
+    float S[SS_R], a[SS_R];
+    float* sp = state + ((int64_t)seq * C + cc) * N;
+#pragma unroll
+    for (int r = 0; r < SS_R; r++) {
+        const int k = s + NS * r;
+        a[r] = k < N ? A[(int64_t)cc * N + k] : 0.f;
+        S[r] = (k < N && !fresh) ? sp[k] : 0.f;
+    }
+    const float dd = D[cc];
+    for (int tile0 = 0; tile0 < n; tile0 += SS_TT) {
+        const int nt = min(SS_TT, n - tile0);
+        const int64_t tb = t0 + tile0;
+        for (int idx = tid; idx < (nt << ch_log2); idx += 128) {
+            const int j = idx >> ch_log2, k = idx & (CH - 1), cg = cbase + k;
+            if (cg < C) {
+                xs[idx] = ldf(x + (tb + j) * x_stride + cg);
+                ds[idx] = softplus_fn(ldf(dtl + (tb + j) * dt_stride + cg) + dt_bias[cg]);
+                zs[idx] = silu_fn(ldf(z + (tb + j) * z_stride + cg));
+            }
+        }
+        for (int idx = tid; idx < nt * N; idx += 128) {
+            const int j = idx / N, k = idx - j * N;
+            const T* br = bc + (tb + j) * bc_stride;
+            bs[idx] = ldf(br + b_off + k);
+            cs[idx] = ldf(br + c_off + k);
+        }
+        __syncthreads();
+        for (int j = 0; j < nt; j++) {
+            const float dt = ds[(j << ch_log2) + cl], xv = xs[(j << ch_log2) + cl];
+            const float dx = dt * xv;
+            float y = 0.f;
+#pragma unroll
+            for (int r = 0; r < SS_R; r++) {
+                const int k = s + NS * r;
+                if (k < N) {
+                    S[r] = expf(dt * a[r]) * S[r] + dx * bs[j * N + k];
+                    y += S[r] * cs[j * N + k];
+                }
+            }
+            for (int o = NS >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+            if (s == 0) ys[(j << ch_log2) + cl] = (y + dd * xv) * zs[(j << ch_log2) + cl];
+        }
+        __syncthreads();
+        for (int idx = tid; idx < (nt << ch_log2); idx += 128) {
+            const int j = idx >> ch_log2, cg = cbase + (idx & (CH - 1));
+            if (cg < C) stf(out + (tb + j) * C + cg, ys[idx]);
+        }
+        // the next tile's staging writes xs / ds / zs / bs / cs, which nobody reads any more; ys is written again only after
+        // the next barrier
+    }
+    if (live) {
+#pragma unroll
+        for (int r = 0; r < SS_R; r++) {
+            const int k = s + NS * r;
+            if (k < N) sp[k] = S[r];
+        }
+    }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
@@ -228,21 +373,33 @@ int sllm_conv_tail_update(const void* xin, int64_t xin_stride, void* tail, const
 }
 
 int sllm_mingru_scan(const void* proj, int64_t proj_stride, void* state, const void* seg_starts, const void* seq_ids,
-                     const void* tok_pos, void* out, int num_segs, int channels, sllm_dtype_t dtype, sllm_stream_t stream) {
+                     const void* tok_pos, void* out, int num_segs, int num_prefill_segs, int channels, sllm_dtype_t dtype,
+                     sllm_stream_t stream) {
     SLLM_REQUIRE(num_segs >= 0 && channels > 0 && proj_stride >= 3 * (int64_t)channels, "mingru_scan: bad shape");
+    SLLM_REQUIRE(num_prefill_segs >= 0 && num_prefill_segs <= num_segs, "mingru_scan: bad number of prompt segments");
     if (num_segs == 0) return 0;
     SLLM_REQUIRE(proj && state && seg_starts && seq_ids && tok_pos && out, "mingru_scan: null pointer");
-    const dim3 grid((unsigned)num_segs, (unsigned)cdiv(channels, 128));
-    SLLM_DISPATCH_DTYPE_F32(dtype, (mingru_scan_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>(
-        (const T*)proj, proj_stride, (float*)state, (const int*)seg_starts, (const int*)seq_ids, (const int*)tok_pos, (T*)out,
-        channels)));
+    if (num_prefill_segs > 0) {
+        const dim3 grid((unsigned)num_prefill_segs, (unsigned)cdiv(channels, 32));
+        SLLM_DISPATCH_DTYPE_F32(dtype, (mingru_scan_tiled_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
+            (const T*)proj, proj_stride, (float*)state, (const int*)seg_starts, (const int*)seq_ids, (const int*)tok_pos, (T*)out,
+            channels)));
+        if (check_launch("mingru_scan (prompt portions)")) return 1;
+    }
+    if (num_segs > num_prefill_segs) {
+        const dim3 grid((unsigned)(num_segs - num_prefill_segs), (unsigned)cdiv(channels, 128));
+        SLLM_DISPATCH_DTYPE_F32(dtype, (mingru_scan_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>(
+            (const T*)proj, proj_stride, (float*)state, (const int*)seg_starts + num_prefill_segs,
+            (const int*)seq_ids + num_prefill_segs, (const int*)tok_pos, (T*)out, channels)));
+    }
     return check_launch("mingru_scan");
 }
 
 int sllm_selective_scan(const void* x, int64_t x_stride, const void* dt, int64_t dt_stride, int dt_f32, const void* dt_bias,
                         const void* A, const void* bc, int64_t bc_stride, int b_off, int c_off, const void* D, const void* z,
                         int64_t z_stride, void* state, const void* seg_starts, const void* seq_ids, const void* tok_pos, void* out,
-                        int num_segs, int channels, int states, sllm_dtype_t dtype, sllm_stream_t stream) {
+                        int num_segs, int num_prefill_segs, int channels, int states, sllm_dtype_t dtype, sllm_stream_t stream) {
+    SLLM_REQUIRE(num_prefill_segs >= 0 && num_prefill_segs <= num_segs, "selective_scan: bad number of prompt segments");
     SLLM_REQUIRE(num_segs >= 0 && channels > 0 && states > 0 && states <= 32 * SS_R, "selective_scan: 1 <= states <= %d (got %d)",
                  32 * SS_R, states);
     if (num_segs == 0) return 0;
@@ -250,14 +407,23 @@ int sllm_selective_scan(const void* x, int64_t x_stride, const void* dt, int64_t
                  "selective_scan: null pointer");
     int ns_log2 = 0;
     while ((SS_R << ns_log2) < states) ns_log2++;
-    const dim3 grid((unsigned)num_segs, (unsigned)cdiv(channels, 128 >> ns_log2));
-#define SS_LAUNCH(TD)                                                                                                          \
-    selective_scan_kernel<T, TD><<<grid, 128, 0, (cudaStream_t)stream>>>(                                                      \
+    const int ch = 128 >> ns_log2;
+    const size_t smem = ((size_t)4 * SS_TT * ch + (size_t)2 * SS_TT * states) * sizeof(float);      // <= 40 KB
+#define SS_LAUNCH(KERNEL, TD, SMEM, SEG0, NSEG)                                                                                \
+    KERNEL<T, TD><<<dim3((unsigned)(NSEG), (unsigned)cdiv(channels, ch)), 128, SMEM, (cudaStream_t)stream>>>(                    \
         (const T*)x, x_stride, (const TD*)dt, dt_stride, (const float*)dt_bias, (const float*)A, (const T*)bc, bc_stride, b_off, \
-        c_off, (const float*)D, (const T*)z, z_stride, (float*)state, (const int*)seg_starts, (const int*)seq_ids,              \
+        c_off, (const float*)D, (const T*)z, z_stride, (float*)state, (const int*)seg_starts + (SEG0), (const int*)seq_ids + (SEG0), \
         (const int*)tok_pos, (T*)out, channels, states, ns_log2)
-    if (dt_f32) { SLLM_DISPATCH_DTYPE_F32(dtype, (SS_LAUNCH(float))); }
-    else { SLLM_DISPATCH_DTYPE_F32(dtype, (SS_LAUNCH(T))); }
+    if (num_prefill_segs > 0) {
+        if (dt_f32) { SLLM_DISPATCH_DTYPE_F32(dtype, (SS_LAUNCH(selective_scan_tiled_kernel, float, smem, 0, num_prefill_segs))); }
+        else { SLLM_DISPATCH_DTYPE_F32(dtype, (SS_LAUNCH(selective_scan_tiled_kernel, T, smem, 0, num_prefill_segs))); }
+        if (check_launch("selective_scan (prompt portions)")) return 1;
+    }
+    if (num_segs > num_prefill_segs) {
+        const int rest = num_segs - num_prefill_segs;
+        if (dt_f32) { SLLM_DISPATCH_DTYPE_F32(dtype, (SS_LAUNCH(selective_scan_kernel, float, 0, num_prefill_segs, rest))); }
+        else { SLLM_DISPATCH_DTYPE_F32(dtype, (SS_LAUNCH(selective_scan_kernel, T, 0, num_prefill_segs, rest))); }
+    }
 #undef SS_LAUNCH
     return check_launch("selective_scan");
 }

@@ -11,6 +11,11 @@ def _stride0(x: torch.Tensor) -> int:
     return x.stride(0) if x.shape[0] > 1 else max(x.stride(0), x.shape[1])
 
 
+def _prefill_segs(st) -> int:
+    """Leading segments of the step that are prompt portions (they take the kernels that tile over time)."""
+    return min(st.batch_size, max(0, int(getattr(st, "num_prefill_seqs", st.batch_size))))
+
+
 def short_conv(xin: torch.Tensor, w: torch.Tensor, bias, tail: torch.Tensor, infer_state, out_dtype: torch.dtype,
                add_input: bool = False, silu: bool = False) -> torch.Tensor:
     """xin [T, C] (fp32 or out_dtype; a column slice is fine), w fp32 [C, taps] (last column: the current token), bias fp32 [C] or
@@ -50,8 +55,8 @@ def mingru_scan(proj: torch.Tensor, state: torch.Tensor, infer_state, channels: 
     st = infer_state
     out = torch.empty((T, C), dtype=proj.dtype, device=proj.device)
     _lib.check(_lib.lib().sllm_mingru_scan(proj.data_ptr(), _stride0(proj), state.data_ptr(), st.seg_starts.data_ptr(),
-                                           st.seq_ids.data_ptr(), st.token_positions.data_ptr(), out.data_ptr(), st.batch_size, C,
-                                           _lib.dtype_tag_f32(proj.dtype), _lib.stream()), "mingru_scan")
+                                           st.seq_ids.data_ptr(), st.token_positions.data_ptr(), out.data_ptr(), st.batch_size,
+                                           _prefill_segs(st), C, _lib.dtype_tag_f32(proj.dtype), _lib.stream()), "mingru_scan")
     return out
 
 
@@ -71,6 +76,6 @@ def selective_scan(x: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, A: 
     _lib.check(_lib.lib().sllm_selective_scan(
         x.data_ptr(), _stride0(x), dt.data_ptr(), _stride0(dt), 1 if dt.dtype == torch.float32 else 0, dt_bias.data_ptr(), A.data_ptr(),
         bc.data_ptr(), _stride0(bc), b_off, c_off, D.data_ptr(), z.data_ptr(), _stride0(z), state.data_ptr(), st.seg_starts.data_ptr(),
-        st.seq_ids.data_ptr(), st.token_positions.data_ptr(), out.data_ptr(), st.batch_size, C, N, _lib.dtype_tag_f32(x.dtype),
-        _lib.stream()), "selective_scan")
+        st.seq_ids.data_ptr(), st.token_positions.data_ptr(), out.data_ptr(), st.batch_size, _prefill_segs(st), C, N,
+        _lib.dtype_tag_f32(x.dtype), _lib.stream()), "selective_scan")
     return out

@@ -133,8 +133,10 @@ def test_short_convolution_with_carried_tail(dtype, C_, K, silu, add, f32_in):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tiled", [True, False])
 @pytest.mark.parametrize("C_", [20, 33, 320, 130])
-def test_mingru_state_through_portions(dtype, C_):
+def test_mingru_state_through_portions(dtype, C_, tiled):
+    """`tiled`: every segment through the kernel that is parallel over time (tiles of 64 tokens), or through the plain one."""
     from swiftllm_b200.worker.kernels.scan_ops import mingru_scan
     g = torch.Generator().manual_seed(C_)
     lens, rows = [150, 37], [2, 0]
@@ -154,6 +156,7 @@ def test_mingru_state_through_portions(dtype, C_):
     got = [[] for _ in lens]
     for segs in _schedule(lens, plan):
         st = _step([(rows[s], p0, n) for s, p0, n in segs])
+        st.num_prefill_seqs = len(segs) if tiled else 0
         x = torch.cat([proj[s][p0:p0 + n] for s, p0, n in segs]).to(DEV)
         out = mingru_scan(x, state, st, C_).float().cpu()
         o = 0
@@ -164,8 +167,10 @@ def test_mingru_state_through_portions(dtype, C_):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tiled", [True, False])
 @pytest.mark.parametrize("C_,N,dt_f32", [(18, 5, True), (7, 40, True), (256, 16, False), (11, 1, True), (40, 200, False), (130, 32, True)])
-def test_selective_scan_state_through_portions(dtype, C_, N, dt_f32):
+def test_selective_scan_state_through_portions(dtype, C_, N, dt_f32, tiled):
+    """`tiled`: every segment through the kernel that stages tiles of tokens in shared memory, or through the plain one."""
     from swiftllm_b200.worker.kernels.scan_ops import selective_scan
     g = torch.Generator().manual_seed(C_ + N)
     lens, rows = [90, 37], [2, 0]
@@ -191,6 +196,7 @@ def test_selective_scan_state_through_portions(dtype, C_, N, dt_f32):
     got = [[] for _ in lens]
     for segs in _schedule(lens, plan):
         st = _step([(rows[s], p0, n) for s, p0, n in segs])
+        st.num_prefill_seqs = len(segs) if tiled else 0
         cat = lambda parts: torch.cat([parts[s][p0:p0 + n] for s, p0, n in segs]).to(DEV)
         out = selective_scan(cat(x), cat(dt), bias.to(DEV), A.to(DEV), cat(bc), R, R + N, D.to(DEV), cat(z), state, st).float().cpu()
         o = 0
@@ -410,6 +416,28 @@ def test_cuda_graph_decode_matches_eager():
     assert runs[0] == runs[1]
     want = B.oracle_greedy(cfg, t, prompts[0], 10)
     assert [s[0] for s in runs[0]] == want
+
+
+def test_memory_profile_then_generation():
+    """The entry point's order of calls: the forged profiling batch (no cache, no state tensors yet) sizes the pool, then the
+    worker generates through the scheduler loop as the oracle does."""
+    from swiftllm_b200.worker.chunking import run_greedy
+    cfg = C.config([(C.attn(), C.moe()), (C.mingru(), None), (C.mamba(), C.dense())], loop=(1, 3, 2))
+    t = O.random_tensors(cfg, seed=19)
+    t["head"] = (t["head"].float() * 4).to(t["head"].dtype)
+    import swiftllm_b200
+    from swiftllm_b200.worker.weight import dict_getter
+    ec = swiftllm_b200.EngineConfig(model_path="", use_dummy=False, block_size=4, gpu_mem_utilization=0.5, num_cpu_blocks=0,
+                                    max_seqs_in_block_table=4, max_blocks_per_seq=16, max_batch_size=4, max_tokens_in_batch=64,
+                                    dtype="float32")
+    m = swiftllm_b200.create_model(ec, swiftllm_b200.registry.model_config_from_dict(cfg))
+    m.load_weights(dict_getter(t))
+    n = m.profile_num_blocks()
+    assert n == 4 * 16                                    # capped by the block table
+    m.init_kvcache_and_swap(n)
+    prompts = [B.tokens_for(cfg, k, 80 + k) for k in (9, 2, 14)]
+    got = run_greedy(m, prompts, new_tokens=4, max_tokens_in_step=10, max_chunk=5, seq_ids=[1, 3, 0])
+    assert got == [B.oracle_greedy(cfg, t, p, 4) for p in prompts]
 
 
 def test_trace_replay_command_line(tmp_path):
