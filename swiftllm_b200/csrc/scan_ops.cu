@@ -19,6 +19,9 @@ constexpr int SC_MAX_TAPS = 8;
 __device__ __forceinline__ float sigmoid_fn(float z) { return 1.f / (1.f + expf(-z)); }
 __device__ __forceinline__ float silu_fn(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplus_fn(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float cvt_f(float v) { return v; }
+__device__ __forceinline__ float cvt_f(__half v) { return __half2float(v); }
+__device__ __forceinline__ float cvt_f(__nv_bfloat16 v) { return __bfloat162float(v); }
 
 // grid (ceil(rows / TOKENS), ceil(C / 128)).  tail: TI [rows, K-1, C] (slot i: the input K-1-i positions before the next one).
 // A thread walks TOKENS consecutive rows of one channel with the last K-1 inputs in registers; where a row does not continue the
@@ -240,26 +243,30 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(
     }
 }
 
-// The same scan for PROMPT PORTIONS with staged tiles of SS_TT tokens: all threads first bring the tile's x, step sizes (softplus
+// The same scan for PROMPT PORTIONS with staged tiles of `tt` tokens (tt * (128 / NS) <= 128 SS_ITEMS: 8 tokens for NS = 1, 16 for
+// NS = 2, 32 from NS = 4 on, fewer when the B / C rows of very wide states would not fit): all threads first bring the tile's x, step sizes (softplus
 // applied), SiLU gates and B / C rows into shared memory with coalesced loads (one exposed load latency per tile instead of one
-// per token), the sequential part then reads shared memory only, and the tile's outputs leave coalesced.  Same thread layout,
-// same arithmetic per step.  Dynamic shared memory: (4 SS_TT (128 / NS) + 2 SS_TT N) floats.
-constexpr int SS_TT = 16;
+// per token), the sequential part then reads shared memory only, and the tile's outputs leave coalesced.  The raw values of the
+// NEXT tile are loaded into registers before the sequential part of the current one and are only touched after it, so their
+// latency hides behind the arithmetic (B / C rows: the first SS_BCR x 128 entries of a tile; wider states load the rest when
+// they stage).  Same thread layout, same arithmetic per step.  Dynamic shared memory: (4 tt (128 / NS) + 2 tt N) floats.
+constexpr int SS_ITEMS = 8;
+constexpr int SS_BCR = 4;
 
 template <typename T, typename TD>
 __global__ void __launch_bounds__(128) selective_scan_tiled_kernel(
     const T* __restrict__ x, int64_t x_stride, const TD* __restrict__ dtl, int64_t dt_stride, const float* __restrict__ dt_bias,
     const float* __restrict__ A, const T* __restrict__ bc, int64_t bc_stride, int b_off, int c_off, const float* __restrict__ D,
     const T* __restrict__ z, int64_t z_stride, float* __restrict__ state, const int* __restrict__ seg_starts,
-    const int* __restrict__ seq_ids, const int* __restrict__ tok_pos, T* __restrict__ out, int C, int N, int ns_log2) {
+    const int* __restrict__ seq_ids, const int* __restrict__ tok_pos, T* __restrict__ out, int C, int N, int ns_log2, int tt) {
     extern __shared__ float ssm[];
     const int NS = 1 << ns_log2, ch_log2 = 7 - ns_log2, CH = 1 << ch_log2;
-    float* xs = ssm;                                    // [SS_TT][CH]
-    float* ds = xs + SS_TT * CH;
-    float* zs = ds + SS_TT * CH;
-    float* ys = zs + SS_TT * CH;
-    float* bs = ys + SS_TT * CH;                        // [SS_TT][N]
-    float* cs = bs + SS_TT * N;
+    float* xs = ssm;                                    // [tt][CH]
+    float* ds = xs + tt * CH;
+    float* zs = ds + tt * CH;
+    float* ys = zs + tt * CH;
+    float* bs = ys + tt * CH;                           // [tt][N]
+    float* cs = bs + tt * N;
     const int b = blockIdx.x, tid = threadIdx.x;
     const int s = tid & (NS - 1), cl = tid >> ns_log2;
     const int cbase = blockIdx.y * CH, c = cbase + cl;
@@ -274,38 +281,74 @@ __global__ void __launch_bounds__(128) selective_scan_tiled_kernel(
 #pragma unroll
     for (int r = 0; r < SS_R; r++) {
         const int k = s + NS * r;
-        a[r] = k < N ? A[(int64_t)cc * N + k] : 0.f;
+        a[r] = k < N ? A[(int64_t)cc * N + k] * 1.4426950408889634f : 0.f;      // exp(dt A) = exp2(dt A log2 e)
         S[r] = (k < N && !fresh) ? sp[k] : 0.f;
     }
     const float dd = D[cc];
-    for (int tile0 = 0; tile0 < n; tile0 += SS_TT) {
-        const int nt = min(SS_TT, n - tile0);
+    // item i of a thread: entry tid + 128 i of the tile.  Kept as loaded: a conversion right behind a load would make the warp wait
+    // for it before the sequential part instead of after
+    T rx[SS_ITEMS], rz[SS_ITEMS], rb[SS_BCR], rc[SS_BCR];
+    TD rd[SS_ITEMS];
+    auto fetch = [&](int tile0) {
+        const int nt = min(tt, n - tile0);                              // <= 0 past the end: nothing is loaded
         const int64_t tb = t0 + tile0;
-        for (int idx = tid; idx < (nt << ch_log2); idx += 128) {
-            const int j = idx >> ch_log2, k = idx & (CH - 1), cg = cbase + k;
-            if (cg < C) {
-                xs[idx] = ldf(x + (tb + j) * x_stride + cg);
-                ds[idx] = softplus_fn(ldf(dtl + (tb + j) * dt_stride + cg) + dt_bias[cg]);
-                zs[idx] = silu_fn(ldf(z + (tb + j) * z_stride + cg));
+#pragma unroll
+        for (int i = 0; i < SS_ITEMS; i++) {
+            const int idx = tid + 128 * i, j = idx >> ch_log2, cg = cbase + (idx & (CH - 1));
+            if (idx < (nt << ch_log2) && cg < C) {
+                rx[i] = x[(tb + j) * x_stride + cg];
+                rd[i] = dtl[(tb + j) * dt_stride + cg];
+                rz[i] = z[(tb + j) * z_stride + cg];
             }
         }
-        for (int idx = tid; idx < nt * N; idx += 128) {
+#pragma unroll
+        for (int i = 0; i < SS_BCR; i++) {
+            const int idx = tid + 128 * i;
+            if (idx < nt * N) {
+                const int j = idx / N, k = idx - j * N;
+                const T* br = bc + (tb + j) * bc_stride;
+                rb[i] = br[b_off + k];
+                rc[i] = br[c_off + k];
+            }
+        }
+    };
+    fetch(0);
+    for (int tile0 = 0; tile0 < n; tile0 += tt) {
+        const int nt = min(tt, n - tile0);
+        const int64_t tb = t0 + tile0;
+#pragma unroll
+        for (int i = 0; i < SS_ITEMS; i++) {
+            const int idx = tid + 128 * i, cg = cbase + (idx & (CH - 1));
+            if (idx < (nt << ch_log2) && cg < C) {
+                xs[idx] = cvt_f(rx[i]);
+                ds[idx] = softplus_fn(cvt_f(rd[i]) + dt_bias[cg]);
+                zs[idx] = silu_fn(cvt_f(rz[i]));
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < SS_BCR; i++) {
+            const int idx = tid + 128 * i;
+            if (idx < nt * N) { bs[idx] = cvt_f(rb[i]); cs[idx] = cvt_f(rc[i]); }
+        }
+        for (int idx = tid + 128 * SS_BCR; idx < nt * N; idx += 128) {
             const int j = idx / N, k = idx - j * N;
             const T* br = bc + (tb + j) * bc_stride;
             bs[idx] = ldf(br + b_off + k);
             cs[idx] = ldf(br + c_off + k);
         }
         __syncthreads();
-        for (int j = 0; j < nt; j++) {
+        fetch(tile0 + tt);                              // in flight during the sequential part below
+        const float* bp = bs + s;
+        const float* cp = cs + s;
+        for (int j = 0; j < nt; j++, bp += N, cp += N) {
             const float dt = ds[(j << ch_log2) + cl], xv = xs[(j << ch_log2) + cl];
             const float dx = dt * xv;
             float y = 0.f;
 #pragma unroll
             for (int r = 0; r < SS_R; r++) {
-                const int k = s + NS * r;
-                if (k < N) {
-                    S[r] = expf(dt * a[r]) * S[r] + dx * bs[j * N + k];
-                    y += S[r] * cs[j * N + k];
+                if (s + NS * r < N) {
+                    S[r] = exp2f(dt * a[r]) * S[r] + dx * bp[NS * r];
+                    y += S[r] * cp[NS * r];
                 }
             }
             for (int o = NS >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
@@ -405,26 +448,49 @@ int sllm_selective_scan(const void* x, int64_t x_stride, const void* dt, int64_t
     if (num_segs == 0) return 0;
     SLLM_REQUIRE(x && dt && dt_bias && A && bc && D && z && state && seg_starts && seq_ids && tok_pos && out,
                  "selective_scan: null pointer");
-    int ns_log2 = 0;
-    while ((SS_R << ns_log2) < states) ns_log2++;
-    const int ch = 128 >> ns_log2;
-    const size_t smem = ((size_t)4 * SS_TT * ch + (size_t)2 * SS_TT * states) * sizeof(float);      // <= 40 KB
-#define SS_LAUNCH(KERNEL, TD, SMEM, SEG0, NSEG)                                                                                \
-    KERNEL<T, TD><<<dim3((unsigned)(NSEG), (unsigned)cdiv(channels, ch)), 128, SMEM, (cudaStream_t)stream>>>(                    \
-        (const T*)x, x_stride, (const TD*)dt, dt_stride, (const float*)dt_bias, (const float*)A, (const T*)bc, bc_stride, b_off, \
-        c_off, (const float*)D, (const T*)z, z_stride, (float*)state, (const int*)seg_starts + (SEG0), (const int*)seq_ids + (SEG0), \
-        (const int*)tok_pos, (T*)out, channels, states, ns_log2)
+    int ns_plain = 0;                                  // lanes per channel (log2): the fewest that hold all states
+    while ((SS_R << ns_plain) < states) ns_plain++;
+    int ns_tiled = ns_plain;
     if (num_prefill_segs > 0) {
-        if (dt_f32) { SLLM_DISPATCH_DTYPE_F32(dtype, (SS_LAUNCH(selective_scan_tiled_kernel, float, smem, 0, num_prefill_segs))); }
-        else { SLLM_DISPATCH_DTYPE_F32(dtype, (SS_LAUNCH(selective_scan_tiled_kernel, T, smem, 0, num_prefill_segs))); }
+        // prompt portions walk their tokens one after the other: with few (segment, channel) pairs more lanes per channel (fewer
+        // states per thread) put more warps on the SMs
+        int sms = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, current_device());
+        while (ns_tiled < 5 && (2 << ns_tiled) <= states &&
+               (((int64_t)num_prefill_segs * channels) << ns_tiled) / 32 < 8 * (int64_t)sms) ns_tiled++;
+    }
+    int tt = SS_ITEMS << ns_tiled;                     // tt * (128 >> ns_tiled) = 128 SS_ITEMS entries per staged array ...
+    if (tt > 32) tt = 32;
+    while (tt > 1 && (size_t)2 * tt * states * sizeof(float) > 24 * 1024) tt >>= 1;                    // ... and B / C rows within 24 KB
+    const size_t smem = ((size_t)4 * tt * (128 >> ns_tiled) + (size_t)2 * tt * states) * sizeof(float);   // <= 40 KB
+#define SS_GRID(NSEG, NSL) dim3((unsigned)(NSEG), (unsigned)cdiv(channels, 128 >> (NSL))), 128
+#define SS_ARGS(TD, SEG0, NSL)                                                                                                 \
+    (const T*)x, x_stride, (const TD*)dt, dt_stride, (const float*)dt_bias, (const float*)A, (const T*)bc, bc_stride, b_off,     \
+        c_off, (const float*)D, (const T*)z, z_stride, (float*)state, (const int*)seg_starts + (SEG0),                          \
+        (const int*)seq_ids + (SEG0), (const int*)tok_pos, (T*)out, channels, states, (NSL)
+    const cudaStream_t st = (cudaStream_t)stream;
+    if (num_prefill_segs > 0) {
+        if (dt_f32) {
+            SLLM_DISPATCH_DTYPE_F32(dtype, (selective_scan_tiled_kernel<T, float><<<SS_GRID(num_prefill_segs, ns_tiled), smem, st>>>(
+                SS_ARGS(float, 0, ns_tiled), tt)));
+        } else {
+            SLLM_DISPATCH_DTYPE_F32(dtype, (selective_scan_tiled_kernel<T, T><<<SS_GRID(num_prefill_segs, ns_tiled), smem, st>>>(
+                SS_ARGS(T, 0, ns_tiled), tt)));
+        }
         if (check_launch("selective_scan (prompt portions)")) return 1;
     }
     if (num_segs > num_prefill_segs) {
         const int rest = num_segs - num_prefill_segs;
-        if (dt_f32) { SLLM_DISPATCH_DTYPE_F32(dtype, (SS_LAUNCH(selective_scan_kernel, float, 0, num_prefill_segs, rest))); }
-        else { SLLM_DISPATCH_DTYPE_F32(dtype, (SS_LAUNCH(selective_scan_kernel, T, 0, num_prefill_segs, rest))); }
+        if (dt_f32) {
+            SLLM_DISPATCH_DTYPE_F32(dtype, (selective_scan_kernel<T, float><<<SS_GRID(rest, ns_plain), 0, st>>>(
+                SS_ARGS(float, num_prefill_segs, ns_plain))));
+        } else {
+            SLLM_DISPATCH_DTYPE_F32(dtype, (selective_scan_kernel<T, T><<<SS_GRID(rest, ns_plain), 0, st>>>(
+                SS_ARGS(T, num_prefill_segs, ns_plain))));
+        }
     }
-#undef SS_LAUNCH
+#undef SS_ARGS
+#undef SS_GRID
     return check_launch("selective_scan");
 }
 
