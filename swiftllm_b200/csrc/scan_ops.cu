@@ -19,6 +19,12 @@ constexpr int SC_MAX_TAPS = 8;
 __device__ __forceinline__ float sigmoid_fn(float z) { return 1.f / (1.f + expf(-z)); }
 __device__ __forceinline__ float silu_fn(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplus_fn(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+// 2^x for x <= 0 on the special-function unit (relative error about 2^-22; results below the normal range become 0)
+__device__ __forceinline__ float exp2_neg(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ float cvt_f(float v) { return v; }
 __device__ __forceinline__ float cvt_f(__half v) { return __half2float(v); }
 __device__ __forceinline__ float cvt_f(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -185,8 +191,8 @@ __global__ void __launch_bounds__(256) mingru_scan_tiled_kernel(const T* __restr
     if (w == 7 && live) state[(int64_t)seq * C + c] = S;
 }
 
-// Block: 128 threads = (128 / NS) channels x NS lanes per channel; a thread holds the states n = s + NS r (r < SS_R) of its
-// channel in registers.  grid (segments, ceil(C / (128 / NS))).  x, z: T [T, C] (row strides); dtl: TD [T, C] step logits (without
+// Block: 128 threads = (128 / NS) channels x NS lanes per channel; lane s of a channel holds the RE = ceil(N / NS) <= SS_R
+// consecutive states n = s RE + r of its channel in registers.  grid (segments, ceil(C / (128 / NS))).  x, z: T [T, C] (row strides); dtl: TD [T, C] step logits (without
 // bias); bc: T [T, ...] rows with B at column b_off and C at column c_off (N each); A fp32 [C, N] (negative); state fp32
 // [rows, C, N].
 constexpr int SS_R = 8;
@@ -197,7 +203,7 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(
     const float* __restrict__ A, const T* __restrict__ bc, int64_t bc_stride, int b_off, int c_off, const float* __restrict__ D,
     const T* __restrict__ z, int64_t z_stride, float* __restrict__ state, const int* __restrict__ seg_starts,
     const int* __restrict__ seq_ids, const int* __restrict__ tok_pos, T* __restrict__ out, int C, int N, int ns_log2) {
-    const int NS = 1 << ns_log2;
+    const int NS = 1 << ns_log2, RE = (N + NS - 1) >> ns_log2;
     const int b = blockIdx.x;
     const int s = threadIdx.x & (NS - 1);
     const int c = blockIdx.y * (blockDim.x >> ns_log2) + (threadIdx.x >> ns_log2);
@@ -211,9 +217,10 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(
     float* sp = state + ((int64_t)seq * C + cc) * N;
 #pragma unroll
     for (int r = 0; r < SS_R; r++) {
-        const int k = s + NS * r;
-        a[r] = k < N ? A[(int64_t)cc * N + k] : 0.f;
-        S[r] = (k < N && !fresh) ? sp[k] : 0.f;
+        const int k = s * RE + r;
+        const bool ok = r < RE && k < N;
+        a[r] = ok ? A[(int64_t)cc * N + k] * 1.4426950408889634f : 0.f;       // exp(dt A) = 2^(dt A log2 e)
+        S[r] = (ok && !fresh) ? sp[k] : 0.f;
     }
     const float bias = dt_bias[cc], dd = D[cc];
     for (int i = 0; i < n; i++) {
@@ -225,9 +232,9 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(
         float y = 0.f;
 #pragma unroll
         for (int r = 0; r < SS_R; r++) {
-            const int k = s + NS * r;
-            if (k < N) {
-                S[r] = expf(dt * a[r]) * S[r] + dx * ldf(br + b_off + k);
+            const int k = s * RE + r;
+            if (r < RE && k < N) {
+                S[r] = exp2_neg(dt * a[r]) * S[r] + dx * ldf(br + b_off + k);
                 y += S[r] * ldf(br + c_off + k);
             }
         }
@@ -237,8 +244,8 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(
     if (live) {
 #pragma unroll
         for (int r = 0; r < SS_R; r++) {
-            const int k = s + NS * r;
-            if (k < N) sp[k] = S[r];
+            const int k = s * RE + r;
+            if (r < RE && k < N) sp[k] = S[r];
         }
     }
 }
@@ -259,8 +266,10 @@ __global__ void __launch_bounds__(128) selective_scan_tiled_kernel(
     const float* __restrict__ A, const T* __restrict__ bc, int64_t bc_stride, int b_off, int c_off, const float* __restrict__ D,
     const T* __restrict__ z, int64_t z_stride, float* __restrict__ state, const int* __restrict__ seg_starts,
     const int* __restrict__ seq_ids, const int* __restrict__ tok_pos, T* __restrict__ out, int C, int N, int ns_log2, int tt) {
-    extern __shared__ float ssm[];
-    const int NS = 1 << ns_log2, ch_log2 = 7 - ns_log2, CH = 1 << ch_log2;
+    extern __shared__ __align__(16) float ssm[];
+    const int NS = 1 << ns_log2, ch_log2 = 7 - ns_log2, CH = 1 << ch_log2, RE = (N + NS - 1) >> ns_log2;
+    // whole groups of four states per lane, on 16-byte boundaries of the staged rows: B and C are read four at a time
+    const bool vec = (N & 3) == 0 && (RE & 3) == 0;
     float* xs = ssm;                                    // [tt][CH]
     float* ds = xs + tt * CH;
     float* zs = ds + tt * CH;
@@ -280,9 +289,10 @@ __global__ void __launch_bounds__(128) selective_scan_tiled_kernel(
     float* sp = state + ((int64_t)seq * C + cc) * N;
 #pragma unroll
     for (int r = 0; r < SS_R; r++) {
-        const int k = s + NS * r;
-        a[r] = k < N ? A[(int64_t)cc * N + k] * 1.4426950408889634f : 0.f;      // exp(dt A) = exp2(dt A log2 e)
-        S[r] = (k < N && !fresh) ? sp[k] : 0.f;
+        const int k = s * RE + r;
+        const bool ok = r < RE && k < N;
+        a[r] = ok ? A[(int64_t)cc * N + k] * 1.4426950408889634f : 0.f;       // exp(dt A) = 2^(dt A log2 e)
+        S[r] = (ok && !fresh) ? sp[k] : 0.f;
     }
     const float dd = D[cc];
     // item i of a thread: entry tid + 128 i of the tile.  Kept as loaded: a conversion right behind a load would make the warp wait
@@ -338,17 +348,32 @@ __global__ void __launch_bounds__(128) selective_scan_tiled_kernel(
         }
         __syncthreads();
         fetch(tile0 + tt);                              // in flight during the sequential part below
-        const float* bp = bs + s;
-        const float* cp = cs + s;
+        const float* bp = bs + s * RE;
+        const float* cp = cs + s * RE;
+        const bool lane_live = s * RE < N;
         for (int j = 0; j < nt; j++, bp += N, cp += N) {
             const float dt = ds[(j << ch_log2) + cl], xv = xs[(j << ch_log2) + cl];
             const float dx = dt * xv;
             float y = 0.f;
+            if (vec) {
 #pragma unroll
-            for (int r = 0; r < SS_R; r++) {
-                if (s + NS * r < N) {
-                    S[r] = exp2f(dt * a[r]) * S[r] + dx * bp[NS * r];
-                    y += S[r] * cp[NS * r];
+                for (int q = 0; q < SS_R / 4; q++) {
+                    if (4 * q < RE && lane_live) {
+                        const float4 b4 = reinterpret_cast<const float4*>(bp)[q], c4 = reinterpret_cast<const float4*>(cp)[q];
+                        S[4 * q + 0] = exp2_neg(dt * a[4 * q + 0]) * S[4 * q + 0] + dx * b4.x;
+                        S[4 * q + 1] = exp2_neg(dt * a[4 * q + 1]) * S[4 * q + 1] + dx * b4.y;
+                        S[4 * q + 2] = exp2_neg(dt * a[4 * q + 2]) * S[4 * q + 2] + dx * b4.z;
+                        S[4 * q + 3] = exp2_neg(dt * a[4 * q + 3]) * S[4 * q + 3] + dx * b4.w;
+                        y += S[4 * q + 0] * c4.x + S[4 * q + 1] * c4.y + S[4 * q + 2] * c4.z + S[4 * q + 3] * c4.w;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < SS_R; r++) {
+                    if (r < RE && s * RE + r < N) {
+                        S[r] = exp2_neg(dt * a[r]) * S[r] + dx * bp[r];
+                        y += S[r] * cp[r];
+                    }
                 }
             }
             for (int o = NS >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
@@ -365,8 +390,8 @@ __global__ void __launch_bounds__(128) selective_scan_tiled_kernel(
     if (live) {
 #pragma unroll
         for (int r = 0; r < SS_R; r++) {
-            const int k = s + NS * r;
-            if (k < N) sp[k] = S[r];
+            const int k = s * RE + r;
+            if (r < RE && k < N) sp[k] = S[r];
         }
     }
 }
