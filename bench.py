@@ -156,14 +156,14 @@ def _arch_models(sz, dtype, only=None):
     # Naforax: [differential attention (heads / 4 KV heads, two maps of 64 per head, values of 128, chunks of 8192 positions) +
     # dense ff], [minGRU of the model's width + experts], [selective scan (inner 2 W, 16 states, 4 taps) + experts], [attention +
     # experts]; experts with a gated shared expert; the middle two layers are the repeated range (one pass: equal depth)
-    nattn = {"heads": H, "kv_heads": G, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.3, "mask": {"size": NAFORAX_CHUNK},
+    nattn = {"heads": H, "kv_heads": G, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.25, "mask": {"size": NAFORAX_CHUNK},
              "rot": {"base": 10000.0, "dims": 32}}
     naf_moe = {"kind": "moe", "expert": {"ff": sz["eff"], "limit": 7.0}, "shared": {"ff": sz["eff"], "limit": 7.0},
                "router": {"experts": sz["experts"], "top": sz["top"]}}
     naf_mixers = [("attention", nattn), ("mingru", {"width": W}),
                   ("mamba1", {"inner": 2 * W, "state": 16, "dt_rank": W // 16, "conv": 4}), ("attention", nattn)]
-    naf = {"architecture": "Naforax", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-5, "groups": 2}, "residual_mult": 0.7,
-           "logit_softcap": 30.0, "canon": {"taps": 3}, "loop": {"start": 1, "stop": 3, "times": 1},
+    naf = {"architecture": "Naforax", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-5, "groups": 4}, "residual_mult": 0.5,
+           "logit_softcap": 30.0, "canon": {"taps": 4}, "loop": {"start": 1, "stop": 3, "times": 1},
            "layers": [{"type": naf_mixers[i % 4][0], "mixer": naf_mixers[i % 4][1],
                        "mlp": {"kind": "dense", "ff": sz["ff"]} if i == 0 else naf_moe} for i in range(sz["layers"])]}
     for name, raw in (("bupozen", bup), ("rivudra", riv), ("buzarax", buz), ("naforax", naf), ("llama", llama)):
@@ -351,7 +351,7 @@ def run_arch_compare(args):
                     "selective_scan": (Ls * ntok * Ci * 7 * Ns, Ls * ntok * Ci * 10, Ls * dec_batch * Ci * 7 * Ns,
                                        Ls * dec_batch * Ci * (10 + 8 * Ns)),
                     "scan_conv": (Ls * ntok * Ci * 8, Ls * ntok * Ci * 4, Ls * dec_batch * Ci * 8, Ls * dec_batch * Ci * (4 + 6)),
-                    "input_conv": (nconv * ntok * Wd * 6, nconv * ntok * Wd * 6, nconv * dec_batch * Wd * 6, nconv * dec_batch * Wd * (6 + 8)),
+                    "input_conv": (nconv * ntok * Wd * 8, nconv * ntok * Wd * 6, nconv * dec_batch * Wd * 8, nconv * dec_batch * Wd * (6 + 24)),
                     "group_norms": (nconv * ntok * Wd * 8, nconv * ntok * Wd * 14, nconv * dec_batch * Wd * 8, nconv * dec_batch * Wd * 14),
                     "diff_combine": (La * ntok * H * dv * 8, La * ntok * H * dv * 12, La * dec_batch * H * dv * 8, La * dec_batch * H * dv * 12),
                 }

@@ -134,7 +134,7 @@ def test_short_convolution_with_carried_tail(dtype, C_, K, silu, add, f32_in):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("tiled", [True, False])
-@pytest.mark.parametrize("C_", [20, 33, 320, 130])
+@pytest.mark.parametrize("C_", [20, 33, 288, 130])
 def test_mingru_state_through_portions(dtype, C_, tiled):
     """`tiled`: every segment through the kernel that is parallel over time (tiles of 64 tokens), or through the plain one."""
     from swiftllm_b200.worker.kernels.scan_ops import mingru_scan
@@ -207,7 +207,7 @@ def test_selective_scan_state_through_portions(dtype, C_, N, dt_f32, tiled):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,G,dv", [(6, 2, 6), (4, 4, 96), (5, 1, 200), (3, 3, 33)])
+@pytest.mark.parametrize("H,G,dv", [(6, 2, 6), (4, 4, 112), (5, 1, 200), (3, 3, 33)])
 def test_two_maps_into_one_gated_head(dtype, H, G, dv):
     from swiftllm_b200.worker.kernels.window_attn import diff_combine
     g = torch.Generator().manual_seed(H + dv)
@@ -221,7 +221,7 @@ def test_two_maps_into_one_gated_head(dtype, H, G, dv):
     assert B.rel_err(out.float(), ref) < _tol(dtype)
 
 
-@pytest.mark.parametrize("H,G,dk,dv,dims,chunk", [(4, 2, 32, 16, 32, 64), (3, 1, 64, 64, 16, 50), (6, 3, 48, 96, 12, 64),
+@pytest.mark.parametrize("H,G,dk,dv,dims,chunk", [(4, 2, 32, 16, 32, 64), (3, 1, 64, 64, 16, 50), (6, 3, 48, 80, 24, 72),
                                                   (4, 4, 16, 128, 0, 37), (2, 2, 128, 32, 64, 300)])
 def test_chunked_two_map_attention_tensor_core_and_cuda_core_agree(H, G, dk, dv, dims, chunk):
     """Norm with weight before interleaved rotary, chunked mask, two key heads per value head, fp32 output: the same mixed step
