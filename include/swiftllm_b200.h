@@ -387,7 +387,9 @@ int sllm_moe_route_softmax(const void* logits, void* weights, int64_t num_tokens
 /* ---- Per-channel recurrences with per-sequence state (new, scan_ops.cu); segments as for the recurrent mixers above.
  * short_conv: out[t, c] = act(bias[c] + sum_k w[c, taps - 1 - k] * xin[t - k, c]) (+ xin[t, c] when add_input); w, bias fp32;
  * xin and tail ([rows, taps - 1, channels]) of in_dtype (SLLM_F32 or out_dtype); act_silu = 1: SiLU.  conv_tail_update moves
- * the tail on by the segments' inputs and runs after every reader of the old tail.
+ * the tail on by the segments' inputs and runs after every reader of the old tail.  move_decode_tails = 1: the rows from
+ * num_prefill_tokens on are one-token segments of sequences that appear once in the step; short_conv moves their tails on itself
+ * (conv_tail_update then only needs the prompt segments).
  * mingru_scan: proj [T, 3 channels] rows [z logits | candidate pre-activations u | gate pre-activations g] (row stride in
  * elements); z = sigmoid, c = u + 1/2 (u >= 0) | sigmoid(u); S <- (1 - z) S + z c; out = S * silu(g); state fp32 [rows, channels].
  * selective_scan: x, z dtype [T, channels]; dt [T, channels] step logits (fp32 when dt_f32, else dtype); bc rows hold B at
@@ -398,7 +400,8 @@ int sllm_moe_route_softmax(const void* logits, void* weights, int64_t num_tokens
  * one thread per channel (and state slice); any value in 0 .. num_segs gives the same result up to rounding. */
 int sllm_short_conv(const void* xin, int64_t xin_stride, sllm_dtype_t in_dtype, const void* w, const void* bias, const void* tail,
                     const void* tok_seq, const void* tok_pos, void* out, sllm_dtype_t out_dtype, int64_t num_tokens,
-                    int64_t num_prefill_tokens, int channels, int taps, int add_input, int act_silu, sllm_stream_t stream);
+                    int64_t num_prefill_tokens, int channels, int taps, int add_input, int act_silu, int move_decode_tails,
+                    sllm_stream_t stream);
 int sllm_conv_tail_update(const void* xin, int64_t xin_stride, void* tail, const void* seg_starts, const void* seq_ids,
                           const void* tok_pos, int num_segs, int channels, int taps, sllm_dtype_t dtype, sllm_stream_t stream);
 int sllm_mingru_scan(const void* proj, int64_t proj_stride, void* state, const void* seg_starts, const void* seq_ids,

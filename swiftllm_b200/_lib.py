@@ -66,7 +66,7 @@ SIGNATURES = {
     "sllm_stream_add": (_I, [_P, _P, _P, _L, _I, _P]),
     "sllm_gelu_glu": (_I, [_P, _P, _L, _I, _I, _P]),
     "sllm_moe_route_softmax": (_I, [_P, _P, _L, _I, _I, _I, _P]),
-    "sllm_short_conv": (_I, [_P, _L, _I, _P, _P, _P, _P, _P, _P, _I, _L, _L, _I, _I, _I, _I, _P]),
+    "sllm_short_conv": (_I, [_P, _L, _I, _P, _P, _P, _P, _P, _P, _I, _L, _L, _I, _I, _I, _I, _I, _P]),
     "sllm_conv_tail_update": (_I, [_P, _L, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "sllm_mingru_scan": (_I, [_P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "sllm_selective_scan": (_I, [_P, _L, _P, _L, _I, _P, _P, _P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),

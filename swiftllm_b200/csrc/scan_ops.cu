@@ -5,7 +5,8 @@
 //
 //   short_conv         out[t, c] = act(b[c] + sum_k w[c, K-1-k] * x[t-k, c]) (+ x[t, c]); inputs before the segment come from the
 //                      sequence's tail (its last K-1 inputs), inputs before position 0 are zero.  Input fp32 or T, output T.
-//   conv_tail_update   moves a sequence's tail on by the segment's inputs (runs after every reader of the old tail)
+//   conv_tail_update   moves a sequence's tail on by the segment's inputs (runs after every reader of the old tail); a decoded
+//                      token's row is the only reader and writer of its sequence's tail, so short_conv moves that tail on itself
 //   mingru_scan        z = sigmoid(zl); c = u + 1/2 (u >= 0) | sigmoid(u) (u < 0); S <- (1 - z) S + z c; out = S * silu(g)
 //   selective_scan     dt = softplus(dtl + bias); S[c, n] <- exp(dt A[c, n]) S[c, n] + dt x B[n]; y = sum_n S C[n] + D x;
 //                      out = y * silu(z)
@@ -33,12 +34,13 @@ __device__ __forceinline__ float cvt_f(__nv_bfloat16 v) { return __bfloat162floa
 // A thread walks TOKENS consecutive rows of one channel with the last K-1 inputs in registers; where a row does not continue the
 // row above (another sequence, or the tile's first row) the window is filled again: from the rows above as far as they are the
 // sequence's previous positions, from the sequence's tail before that, zeros before position 0.
+// TOKENS = 1 with move_tail: every row is a one-token segment of its own sequence; its thread then writes the sequence's new tail.
 template <typename TI, typename TO, int TOKENS>
 __global__ void __launch_bounds__(128) short_conv_kernel(const TI* __restrict__ xin, int64_t xin_stride, const float* __restrict__ w,
-                                                         const float* __restrict__ bias, const TI* __restrict__ tail,
+                                                         const float* __restrict__ bias, TI* tail,
                                                          const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                                                          TO* __restrict__ out, int64_t row0, int64_t row_end, int C, int K,
-                                                         int add_input, int act_silu) {
+                                                         int add_input, int act_silu, int move_tail) {
     const int64_t tile0 = row0 + (int64_t)blockIdx.x * TOKENS;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= C) return;
@@ -78,6 +80,12 @@ __global__ void __launch_bounds__(128) short_conv_kernel(const TI* __restrict__ 
         for (int k = SC_MAX_TAPS - 1; k >= 1; k--) hist[k] = hist[k - 1];
         hist[0] = xv[i];
         prev_seq = seq; prev_pos = pos;
+        if (TOKENS == 1 && move_tail) {                 // slot i <- the input K - 2 - i positions back (zeros before position 0)
+            TI* tl = tail + (int64_t)seq * (K - 1) * C + c;
+#pragma unroll
+            for (int k = 0; k < SC_MAX_TAPS - 1; k++)
+                if (k < K - 1) stf(tl + (int64_t)(K - 2 - k) * C, hist[k]);
+        }
     }
 }
 
@@ -404,7 +412,8 @@ extern "C" {
 
 int sllm_short_conv(const void* xin, int64_t xin_stride, sllm_dtype_t in_dtype, const void* w, const void* bias, const void* tail,
                     const void* tok_seq, const void* tok_pos, void* out, sllm_dtype_t out_dtype, int64_t num_tokens,
-                    int64_t num_prefill_tokens, int channels, int taps, int add_input, int act_silu, sllm_stream_t stream) {
+                    int64_t num_prefill_tokens, int channels, int taps, int add_input, int act_silu, int move_decode_tails,
+                    sllm_stream_t stream) {
     SLLM_REQUIRE(num_tokens >= 0 && channels > 0 && taps >= 1 && taps <= SC_MAX_TAPS, "short_conv: 1 <= taps <= %d (got %d)",
                  SC_MAX_TAPS, taps);
     SLLM_REQUIRE(num_prefill_tokens >= 0 && num_prefill_tokens <= num_tokens, "short_conv: bad number of prompt rows");
@@ -414,8 +423,9 @@ int sllm_short_conv(const void* xin, int64_t xin_stride, sllm_dtype_t in_dtype, 
     const cudaStream_t st = (cudaStream_t)stream;
 #define SC_LAUNCH(TI, TOKENS, r0, r1)                                                                                          \
     short_conv_kernel<TI, T, TOKENS><<<dim3((unsigned)cdiv((r1) - (r0), TOKENS), (unsigned)cdiv(channels, 128)), 128, 0, st>>>(   \
-        (const TI*)xin, xin_stride, (const float*)w, (const float*)bias, (const TI*)tail, (const int*)tok_seq,                  \
-        (const int*)tok_pos, (T*)out, (int64_t)(r0), (int64_t)(r1), channels, taps, add_input, act_silu)
+        (const TI*)xin, xin_stride, (const float*)w, (const float*)bias, (TI*)tail, (const int*)tok_seq,                        \
+        (const int*)tok_pos, (T*)out, (int64_t)(r0), (int64_t)(r1), channels, taps, add_input, act_silu,                        \
+        (TOKENS == 1 && move_decode_tails && taps > 1) ? 1 : 0)
     if (num_prefill_tokens > 0) {
         if (in_dtype == SLLM_F32) { SLLM_DISPATCH_DTYPE_F32(out_dtype, (SC_LAUNCH(float, 16, 0, num_prefill_tokens))); }
         else { SLLM_DISPATCH_DTYPE_F32(out_dtype, (SC_LAUNCH(T, 16, 0, num_prefill_tokens))); }

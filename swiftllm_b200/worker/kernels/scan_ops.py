@@ -17,9 +17,11 @@ def _prefill_segs(st) -> int:
 
 
 def short_conv(xin: torch.Tensor, w: torch.Tensor, bias, tail: torch.Tensor, infer_state, out_dtype: torch.dtype,
-               add_input: bool = False, silu: bool = False) -> torch.Tensor:
+               add_input: bool = False, silu: bool = False, move_tail: bool = False) -> torch.Tensor:
     """xin [T, C] (fp32 or out_dtype; a column slice is fine), w fp32 [C, taps] (last column: the current token), bias fp32 [C] or
-    None, tail [rows, taps - 1, C] of xin's dtype -> [T, C] out_dtype = act(conv(xin)) (+ xin).  The tail is only read."""
+    None, tail [rows, taps - 1, C] of xin's dtype -> [T, C] out_dtype = act(conv(xin)) (+ xin).  move_tail: every sequence's tail
+    moves on by the step's inputs - decoded tokens' inside the convolution kernel, prompt portions' in a launch of their own
+    behind it; otherwise the tail is only read."""
     T, C = xin.shape
     taps = w.shape[1]
     assert xin.stride(1) == 1 and w.is_contiguous() and w.shape[0] == C and w.dtype == torch.float32
@@ -31,18 +33,22 @@ def short_conv(xin: torch.Tensor, w: torch.Tensor, bias, tail: torch.Tensor, inf
     _lib.check(_lib.lib().sllm_short_conv(xin.data_ptr(), _stride0(xin), _lib.dtype_tag_f32(xin.dtype), w.data_ptr(), _lib.ptr(bias),
                                           _lib.ptr(tail), infer_state.token_seq_ids.data_ptr(), infer_state.token_positions.data_ptr(),
                                           out.data_ptr(), _lib.dtype_tag_f32(out_dtype), T, npre, C, taps, 1 if add_input else 0,
-                                          1 if silu else 0, _lib.stream()), "short_conv")
+                                          1 if silu else 0, 1 if move_tail else 0, _lib.stream()), "short_conv")
+    if move_tail and taps > 1 and _prefill_segs(infer_state) > 0:
+        conv_tail_update(xin, tail, infer_state, _prefill_segs(infer_state))
     return out
 
 
-def conv_tail_update(xin: torch.Tensor, tail: torch.Tensor, infer_state):
-    """tail [rows, taps - 1, C] <- every segment's sequence's last taps - 1 inputs after the step (xin [T, C], same dtype)."""
+def conv_tail_update(xin: torch.Tensor, tail: torch.Tensor, infer_state, num_segs: int = None):
+    """tail [rows, taps - 1, C] <- the sequences' last taps - 1 inputs after the step (xin [T, C], same dtype), for the step's
+    first num_segs segments (default: all)."""
     C, taps = xin.shape[1], tail.shape[1] + 1
     assert xin.stride(1) == 1 and tail.is_contiguous() and tail.dtype == xin.dtype and tail.shape[2] == C
     _lib.require_device(xin)
     st = infer_state
     _lib.check(_lib.lib().sllm_conv_tail_update(xin.data_ptr(), _stride0(xin), tail.data_ptr(), st.seg_starts.data_ptr(),
-                                                st.seq_ids.data_ptr(), st.token_positions.data_ptr(), st.batch_size, C, taps,
+                                                st.seq_ids.data_ptr(), st.token_positions.data_ptr(),
+                                                st.batch_size if num_segs is None else num_segs, C, taps,
                                                 _lib.dtype_tag_f32(xin.dtype), _lib.stream()), "conv_tail_update")
 
 

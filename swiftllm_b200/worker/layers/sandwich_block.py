@@ -7,7 +7,7 @@ import torch
 
 from swiftllm_b200.model_config import MinGruSpec, SelectiveScanSpec
 from swiftllm_b200.worker.kernels.sandwich_ops import group_norm_add_norm
-from swiftllm_b200.worker.kernels.scan_ops import conv_tail_update, short_conv
+from swiftllm_b200.worker.kernels.scan_ops import short_conv
 from swiftllm_b200.worker.layers.feed_forward import build_feed_forward
 from swiftllm_b200.worker.layers.min_gru import MinGruMixer
 from swiftllm_b200.worker.layers.selective_scan import SelectiveScanMixer
@@ -44,10 +44,7 @@ class SandwichBlockLayer:
         if st.ignore_kvcache:
             return n.to(dtype)
         tail = states[tail_name] if self.taps > 1 else None
-        h = short_conv(n, taps_w, None, tail, st, dtype, add_input=True)
-        if tail is not None:
-            conv_tail_update(n, tail, st)
-        return h
+        return short_conv(n, taps_w, None, tail, st, dtype, add_input=True, move_tail=True)
 
     def forward(self, x, n, caches, block_table, states, st, next_norm=None):
         """x fp32 [T, W] (in place); n = norm1(x) fp32; next_norm: weight of the norm that reads the result (or None).

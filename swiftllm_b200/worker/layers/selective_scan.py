@@ -4,7 +4,7 @@ update, read-out, D skip, SiLU gate of z: one kernel, fp32 state [inner, state] 
 import torch
 
 from swiftllm_b200.worker.kernels.linear import linear, linear_f32_out
-from swiftllm_b200.worker.kernels.scan_ops import conv_tail_update, selective_scan, short_conv
+from swiftllm_b200.worker.kernels.scan_ops import selective_scan, short_conv
 
 
 class SelectiveScanMixer:
@@ -30,9 +30,7 @@ class SelectiveScanMixer:
             return linear(xz[:, :C], w.o)
         xin, z = xz[:, :C], xz[:, C:]
         tail = states[self.tail_name] if m.conv > 1 else None
-        x = short_conv(xin, w.conv, w.conv_b, tail, st, h.dtype, silu=True)
-        if tail is not None:
-            conv_tail_update(xin, tail, st)
+        x = short_conv(xin, w.conv, w.conv_b, tail, st, h.dtype, silu=True, move_tail=True)
         proj = linear(x, w.x_proj)                                          # [T, dt (R) | B (N) | C (N)]
         dt = linear_f32_out(proj[:, :R], w.dt_proj)                         # step logits, fp32 [T, C]
         y = selective_scan(x, dt, w.dt_bias, w.A, proj, R, R + N, w.D, z, states[self.state_name], st)

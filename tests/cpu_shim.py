@@ -362,7 +362,7 @@ def _linear_f32_out(a, w):
     return a.float() @ w.float().t()
 
 
-def _short_conv(xin, w, bias, tail, st, out_dtype, add_input=False, silu=False):
+def _short_conv(xin, w, bias, tail, st, out_dtype, add_input=False, silu=False, move_tail=False):
     T, C = xin.shape
     K = w.shape[1]
     xf = xin.float()
@@ -379,6 +379,8 @@ def _short_conv(xin, w, bias, tail, st, out_dtype, add_input=False, silu=False):
             if silu:
                 acc = torch.nn.functional.silu(acc)
             out[t] = acc + (xf[t] if add_input else 0.0)
+    if move_tail and K > 1:
+        _conv_tail_update(xin, tail, st)
     return out.to(out_dtype)
 
 
@@ -621,9 +623,7 @@ _PATCHES = [
     ("swiftllm_b200.worker.naforax_model", "stream_add", _stream_add),
     ("swiftllm_b200.worker.layers.sandwich_block", "group_norm_add_norm", _group_norm_add_norm),
     ("swiftllm_b200.worker.layers.sandwich_block", "short_conv", _short_conv),
-    ("swiftllm_b200.worker.layers.sandwich_block", "conv_tail_update", _conv_tail_update),
     ("swiftllm_b200.worker.layers.selective_scan", "short_conv", _short_conv),
-    ("swiftllm_b200.worker.layers.selective_scan", "conv_tail_update", _conv_tail_update),
     ("swiftllm_b200.worker.layers.selective_scan", "selective_scan", _selective_scan),
     ("swiftllm_b200.worker.layers.selective_scan", "linear_f32_out", _linear_f32_out),
     ("swiftllm_b200.worker.layers.min_gru", "mingru_scan", _mingru_scan),

@@ -116,6 +116,10 @@ def test_state_rows_used_again(cpu):
     C.case_state_rows_used_again(cpu)
 
 
+def test_long_decode(cpu):
+    B.case_long_decode(cpu, C.config([(C.attn(chunk=11), C.dense()), (C.mingru(), None), (C.mamba(), C.moe())], loop=(0, 2, 2)), n=45)
+
+
 def test_greedy_generation(cpu):
     B.case_greedy_generation(cpu, C.config([(C.mingru(), C.moe()), (C.attn(), C.dense()), (C.mamba(), None)], loop=(0, 2, 2)))
 

@@ -98,8 +98,10 @@ def test_clamped_experts_with_a_gated_shared_expert(dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("C_,K,silu,add,f32_in", [(24, 4, False, True, True), (33, 1, False, True, True), (20, 2, True, False, False),
                                                    (192, 3, True, False, False), (130, 8, False, True, True)])
-def test_short_convolution_with_carried_tail(dtype, C_, K, silu, add, f32_in):
-    """Two sequences in rows 2 and 0 of the tail tensor (which starts full of junk), fed in portions down to one token."""
+@pytest.mark.parametrize("fused", [False, True])
+def test_short_convolution_with_carried_tail(dtype, C_, K, silu, add, f32_in, fused):
+    """Two sequences in rows 2 and 0 of the tail tensor (which starts full of junk), fed in portions down to one token.
+    `fused`: the convolution moves the tails on itself (decoded rows inside its kernel), else a separate call does."""
     from swiftllm_b200.worker.kernels.scan_ops import conv_tail_update, short_conv
     g = torch.Generator().manual_seed(C_ + K)
     lens, rows = [150, 37], [2, 0]
@@ -119,10 +121,11 @@ def test_short_convolution_with_carried_tail(dtype, C_, K, silu, add, f32_in):
         order = sorted(segs, key=lambda e: e[2] == 1)                  # prompt portions first
         st = _step([(rows[s], p0, n) for s, p0, n in order])
         st.num_prefill_tokens = sum(n for _, _, n in order if n > 1)
+        st.num_prefill_seqs = sum(1 for _, _, n in order if n > 1)
         x = torch.cat([xin[s][p0:p0 + n] for s, p0, n in order]).to(DEV)
         out = short_conv(x, w.to(DEV), None if bias is None else bias.to(DEV), tail if K > 1 else None, st, dtype, add_input=add,
-                         silu=silu).float().cpu()
-        if K > 1:
+                         silu=silu, move_tail=fused).float().cpu()
+        if K > 1 and not fused:
             conv_tail_update(x, tail, st)
         o = 0
         for s, p0, n in order:
