@@ -4,7 +4,7 @@ owns ONE row - its block-table row - of each state tensor for as long as it live
 with the same `seq_ids`.
 
 Rows are used again without being cleared: the kernels that read a state take the zero state for a segment that starts at
-position 0 (csrc/recurrent.cu, csrc/stream_ops.cu), so a new sequence never sees what the row's previous owner left, and
+position 0 (csrc/recurrent.cu, csrc/scan_ops.cu, csrc/stream_ops.cu), so a new sequence never sees what the row's previous owner left, and
 freeing a sequence costs nothing here."""
 from __future__ import annotations
 

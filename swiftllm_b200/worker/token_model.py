@@ -2,7 +2,8 @@
 position): the public surface of `LlamaModel` (worker/model.py), the paged cache tensors and their block manager, per-sequence
 recurrent state (worker/state_manager.py), the step's metadata and angle tables, and the CUDA-graph replay of pure-decode steps.
 A topology subclasses it (worker/parallel_block_model.py: parallel blocks; worker/buzarax_model.py: sequential blocks whose
-sublayer outputs are normalised, with recurrent mixers) and provides `_load_weights`, `_build_layers` and `_forward`.
+sublayer outputs are normalised, with recurrent mixers; worker/naforax_model.py: sequential blocks with norms on both sides of
+every sublayer, of which a range of layers runs several times) and provides `_load_weights`, `_build_layers` and `_forward`.
 
     Model(engine_config[, model_config]) -> load_weights() -> profile_num_blocks() -> init_kvcache_and_swap(num_blocks)
     forward(input_ids_list, seq_ids_list, decoding_seq_lens_list, ignore_kvcache=False, prefill_prefix_lens_list=None,
